@@ -53,6 +53,8 @@ class LayerSpec:
     # tensor-name component of each part below the prefix, as (part, name) pairs:
     # ("norm1", "input_layernorm"), ("mixer", "self_attn"), ...
     names: Tuple[Tuple[str, str], ...] = ()
+    # constructor arguments of the arrangement itself, as (name, value) pairs
+    arrangement_params: Tuple[Tuple[str, Any], ...] = ()
 
     def name_of(self, part: str) -> str:
         return self.prefix + dict(self.names)[part] + "."
@@ -98,6 +100,10 @@ class ModelPlan:
     stream_vectors: Tuple[Tuple[str, int], ...] = ()
     # parts of the "embedding" registry whose rows are added to the token embedding
     embedding_extras: Tuple[PartSpec, ...] = ()
+    # residual streams a token (the blocks' arrangement reads and writes all of them; they start as
+    # copies of the embedding and the last norm reads their sum)
+    streams: int = 1
+    logit_softcap: float = 0.0                                  # > 0: logits <- cap * tanh(logits / cap)
 
 
 # --------------------------------------------------------------------------------------

@@ -325,11 +325,14 @@ def tensor_core_status() -> int:
 def index_status() -> int:
     """0, or what a kernel that follows device-side indices found outside its operands since the
     last call (it skips such an access): 201-203 the streaming product (group, row range, row
-    index), 300 + token + 1 the combine, 100000 + row + 1 a decode-attention row whose position
+    index), 300 + token + 1 the combine, 400 an expert table's entry that names no expert, 100000 + row + 1 a decode-attention row whose position
     lay beyond the key blocks its call allowed for.  Synchronises the device."""
     lib = _lib.load()
     sk, cb = int(lib.nf_skinny_index_status()), int(lib.nf_combine_index_status())
     da = int(lib.nf_decode_attention_status())
+    tr = int(lib.nf_table_route_status())
+    if tr:
+        return 400
     return 200 + sk if sk else (300 + cb if cb else (100000 + da if da else 0))
 
 
@@ -1390,6 +1393,174 @@ def latent_attention(q_abs: torch.Tensor, q: torch.Tensor, head_stride: int, rot
 # ---------------------------------------------------------------------------------------
 # sampling
 # ---------------------------------------------------------------------------------------
+
+# ---------------------------------------------------------------------------------------
+# several residual streams a token, the norm in groups
+# ---------------------------------------------------------------------------------------
+
+MAX_STREAMS = 8
+
+
+def embed_copies(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, copies: int) -> None:
+    """out[t, c] = float32(table[ids[t]]) for c < copies; out is [T, copies * hidden]."""
+    _chk(table, "table"); _chk(ids, "ids", torch.int32); _chk(out, "out", torch.float32)
+    _lib.call("nf_embed_copies", _p(table), _p(ids), _p(out), c_int(ids.numel()), c_int(table.shape[1]),
+              c_int(table.shape[0]), c_int(copies), c_int(_dt(table)), _stream())
+
+
+def streams_mix_norm(streams: torch.Tensor, S: int, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                     out_w: Optional[torch.Tensor], in_w: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                     eps: float, groups: int, out_dtype: Optional[torch.dtype],
+                     rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """What lies between two sublayers of a token with S residual streams (float32 [T, S * hidden]):
+
+        x_t <- sum_s mix[s, t] x_s + out_w[t] * y     (if y is given; written back unless `rows`)
+        u = sum_t in_w[t] x_t                         (in_w None: the plain sum)
+        returns u / rms-in-groups(u) * weight         in `out_dtype` (None: only the update is applied)
+
+    `mix` None is the identity, `out_w` None ones: with S = 1 that is the ordinary residual sum.  With
+    `rows`, row r of the result belongs to token rows[r] and the streams are left as they are."""
+    _chk(streams, "streams", torch.float32)
+    T, SW = streams.shape
+    hidden = SW // S
+    for name, v in (("mix", mix), ("out_w", out_w), ("in_w", in_w), ("weight", weight)):
+        if v is not None:
+            _chk(v, name, torch.float32)
+    R = T
+    if rows is not None:
+        _chk(rows, "rows", torch.int32)
+        R = rows.numel()
+    normed = None
+    if out_dtype is not None:
+        normed = torch.empty((R, hidden), dtype=out_dtype, device=streams.device)
+    if y is not None:
+        _chk(y, "y")
+        if out_dtype is not None and y.dtype != out_dtype:
+            raise TypeError("streams_mix_norm: y and the normed rows have one type")
+    dt = _dt(normed) if normed is not None else (_dt(y) if y is not None else 0)
+    _lib.call("nf_streams_mix_norm", _p(streams), _p(y), _p(rows), _p(mix), _p(out_w), _p(in_w), _p(weight),
+              c_float(eps), c_int(groups), _p(normed), c_int(R), c_int(S), c_int(hidden),
+              c_int(0 if rows is not None else 1), c_int(dt), _stream())
+    return normed
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap), in place (float32)."""
+    _chk(x, "x", torch.float32)
+    _lib.call("nf_softcap", _p(x), c_longlong(x.numel()), c_float(cap), _stream())
+
+
+# ---------------------------------------------------------------------------------------
+# attention whose heads' scores are mixed, over chunks, with a sink
+# ---------------------------------------------------------------------------------------
+
+def head_norm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor],
+                          k_norm: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot: int,
+                          ctx, H: int, G: int, D: int, Dv: int, pages: Optional[torch.Tensor],
+                          block_table: Optional[torch.Tensor], page_size: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """proj float32 [T, H*D | G*D | G*Dv] (+ bias): queries and keys normed per head (weights [D] shared
+    by the heads) and turned over their first `rot` dimensions; returns the queries [T, H*D] in
+    `out_dtype` and writes row [k | v] of every token into its page ([pages, page_size, G*(D+Dv)]).
+    G = 0: the queries alone."""
+    _chk(proj, "proj", torch.float32)
+    T = proj.shape[0]
+    q = torch.empty((T, H * D), dtype=out_dtype, device=proj.device)
+    if G:
+        _chk(pages, "pages", out_dtype)
+    _lib.call("nf_head_norm_rope_append", _p(proj), c_int(proj.shape[1]), _p(bias), _p(q_norm), _p(k_norm),
+              c_float(eps), _p(inv_freq), c_int(rot), _p(ctx.positions), _p(ctx.row_seg), _p(q),
+              _p(pages) if G else None, _p(block_table) if G else None,
+              c_int(block_table.shape[1] if G else 0), c_int(T), c_int(H), c_int(G), c_int(D), c_int(Dv),
+              c_int(page_size), c_int(pages.shape[0] if G else 0), c_int(_dt(q)), _stream())
+    return q
+
+
+def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: torch.Tensor,
+                      block_table: torch.Tensor, page_size: int, ctx, chunk: int, scale: float,
+                      talk: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """q [T, H*D] against the paged rows [k | v] -> [T, H*Dv].  Scores of all heads of a (row, key)
+    pair are mixed by `talk` [H, H] before the softmax; key j is seen from position i iff j <= i and,
+    with `chunk` > 0, i // chunk == j // chunk; `sink` [H] adds exp(sink_h) to the denominator."""
+    _chk(q, "q"); _chk(pages, "pages", q.dtype)
+    T = q.shape[0]
+    out = torch.empty((T, H * Dv), dtype=q.dtype, device=q.device)
+    _lib.call("nf_talking_attention", _p(q), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+              _p(ctx.positions), _p(ctx.row_seg), None, _p(talk), _p(sink), _p(out), c_int(T), c_int(H), c_int(G),
+              c_int(D), c_int(Dv), c_int(page_size), c_int(pages.shape[0]), c_int(chunk), c_float(scale),
+              c_int(_dt(q)), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# feed-forwards without a gate
+# ---------------------------------------------------------------------------------------
+
+def poly_norm_act(z: torch.Tensor, coef: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """z float32 [T, n] -> coef[0] N(z) + coef[1] N(z^2) + coef[2] N(z^3) + coef[3], N = the row divided
+    by its root mean square."""
+    _chk(z, "z", torch.float32); _chk(coef, "coef", torch.float32)
+    out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+    _lib.call("nf_poly_norm_act", _p(z), _p(coef), c_float(eps), _p(out), c_int(z.shape[0]), c_int(z.shape[1]),
+              c_int(_dt(out)), _stream())
+    return out
+
+
+def add_bias_rows(y: torch.Tensor, bias: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y float32 [T, n] + bias [n] -> `out_dtype`: the bias meets the projection's unrounded sums."""
+    _chk(y, "y", torch.float32); _chk(bias, "bias", torch.float32)
+    out = torch.empty(y.shape, dtype=out_dtype, device=y.device)
+    _lib.call("nf_add_bias_rows", _p(y), _p(bias), _p(out), c_int(y.shape[0]), c_int(y.shape[1]), c_int(_dt(out)),
+              _stream())
+    return out
+
+
+def gelu_erf_(x: torch.Tensor) -> torch.Tensor:
+    """The exact GELU, in place."""
+    _chk(x, "x")
+    _lib.call("nf_gelu_erf", _p(x), c_longlong(x.numel()), c_int(_dt(x)), _stream())
+    return x
+
+
+def table_route(table: torch.Tensor, ids: torch.Tensor, E: int) -> torch.Tensor:
+    """int32 [T, k]: row ids[t] of the experts' table [rows, k]."""
+    _chk(table, "table", torch.int32); _chk(ids, "ids", torch.int32)
+    T, k = ids.numel(), table.shape[1]
+    idx = torch.empty((T, k), dtype=torch.int32, device=ids.device)
+    _lib.call("nf_table_route", _p(table), _p(ids), _p(idx), c_int(T), c_int(k), c_int(table.shape[0]), c_int(E),
+              _stream())
+    return idx
+
+
+def moe_rows_gemm(x: torch.Tensor, w, plan: "MoePlan", k: int, from_tokens: bool) -> torch.Tensor:
+    """One ungated product of the routed experts: sorted pair p of expert e -> x_p W_e^T.  With
+    `from_tokens`, x is [T, K] and pair p reads token order[p] // k; otherwise x is [T*k, K] in
+    sorted order.  `w` is [E, N, K] or its packed form."""
+    if not from_tokens:
+        return moe_gemm2(x, w, plan, plan_is_older=True)
+    _chk(x, "x")
+    T, K = x.shape
+    packed = isinstance(w, PackedWeights)
+    if packed and T > TUNING["skinny_moe_max_tokens"]:
+        return moe_gemm2(moe_gather(x, plan, k), w, plan, plan_is_older=True)
+    if packed:
+        E, N = w.groups, w.n_features
+    else:
+        _chk(w, "w", x.dtype)
+        E, N, _ = w.shape
+    out = torch.empty((T * k, N), dtype=x.dtype, device=x.device)
+    if T == 0:
+        return out
+    if packed:
+        _skinny(x, K, w.data, w.group_stride, out, T * k, N, K, E, T, plan.offsets, plan.order, k, False,
+                packed=True, group_map=plan.active)
+        return out
+    path = "simt" if x.dtype == torch.float32 else _bf16_path(T, K, "bf16_moe")
+    if path == "skinny":
+        _skinny(x, K, w, N * K, out, T * k, N, K, E, T, plan.offsets, plan.order, k, False, group_map=plan.active)
+    else:
+        _gemm_simt(x, K, w, N * K, out, T * k, N, K, E, T, plan.offsets, plan.order, k, False)
+    return out
+
 
 SAMPLE_MAX_TOP_K = 1024
 

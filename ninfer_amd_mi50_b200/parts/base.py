@@ -32,7 +32,7 @@ class TensorSpec:
            "router" - routing matrices, held in float32 for the same reason;
            "table"  - integer tables, held as int32.
     init:  distribution for the random-weights mode: "linear" N(0, 0.02),
-           "norm" 1 + N(0, 0.05).
+           "norm" 1 + N(0, 0.05); for a table "distinct:<n>": rows of different numbers below n.
     """
     name: str
     shape: Tuple[int, ...]
@@ -330,12 +330,27 @@ class BiasedOutput:
     bias: torch.Tensor
 
 
+@dataclass
+class StreamUpdate:
+    """What a block over several residual streams leaves pending: its last sublayer's output `y`
+    [T, hidden] with the constants of the update ``x_t <- sum_s mix[s, t] x_s + out[t] * y``
+    (`mix` None: the identity; `out` None: ones).  Whoever reads the streams next applies it in its
+    own pass over them (`kernels.streams_mix_norm`)."""
+    y: torch.Tensor
+    mix: Optional[torch.Tensor]
+    out: Optional[torch.Tensor]
+
+
 def summed(delta):
     """`delta` as a tensor (None stays None; a `StreamCopy` means nothing is left to add)."""
     if isinstance(delta, StreamCopy):
         return None
     if isinstance(delta, BiasedOutput):
         return delta.y + delta.bias.to(delta.y.dtype)
+    if isinstance(delta, StreamUpdate):
+        if delta.mix is not None or delta.out is not None:
+            raise TypeError("an update of several residual streams cannot be read as one sum")
+        return delta.y
     return delta.materialize() if isinstance(delta, RoutedSum) else delta
 
 
@@ -431,6 +446,17 @@ class Block(Part):
 
     def state_spec(self) -> Optional[StateSpec]:
         return self.mixer.state_spec()
+
+    def settle(self, h: torch.Tensor, pending):
+        """Add what this block's `forward` left pending to the stream now; returns what is then left
+        (None, or the `StreamCopy` of an arrangement that leaves nothing).  For looking at the
+        stream between layers; the step itself never calls it."""
+        if isinstance(pending, StreamCopy):
+            return pending
+        delta = summed(pending)
+        if delta is not None:
+            h.add_(delta.to(torch.float32))
+        return None
 
     def forward(self, h: torch.Tensor, pending, ctx: StepContext,
                 cache: Optional[CacheView], state: Optional[torch.Tensor]):

@@ -134,3 +134,114 @@ class SublayerNormScaledBlock(Block):
                 f, bias = f.y, f.bias
             x = self.norm2.add_scaled_norm(h, f, self.scale2, copy_dtype, bias=bias)
         return StreamCopy(x)
+
+
+@register_part("block", "hyper_connections")
+class HyperConnectionBlock(Block):
+    """Pre-norm sublayers over several residual streams a token.  For sublayer q (1: mixer, 2:
+    feed-forward) with its constants in_q [S], out_q [S], mix_q [S, S] (indexed [from, to]):
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] * y
+
+    all streams at once from the old ones.  The stream tensor is ``[T, S * width]``; the update of
+    one sublayer, the read for the next and its norm are one kernel, so the last update of a block is
+    left pending (`StreamUpdate`) for whoever reads the streams next.  With `learned` false there are
+    no tensors and in = out = 1, mix = identity: for S = 1 that is the ordinary pre-norm residual
+    block.  The norms are asked for their weight, groups and eps; the kernel does the arithmetic.
+    """
+
+    wants_spec = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward, spec=None,
+                 streams: int = 1, learned: bool = True, tensor_names=None):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        self.streams, self.learned = int(streams), bool(learned)
+        if self.streams < 1:
+            raise ValueError("a token has at least one residual stream")
+        if not self.learned and self.streams != 1:
+            raise ValueError("several residual streams need their constants")
+        for n in (norm1, norm2):
+            if not all(hasattr(n, a) for a in ("weight", "eps", "size")):
+                raise TypeError("the arrangement over several streams takes norms that are an RMS norm with a weight")
+        names = dict(spec.names) if spec is not None else {}
+        prefix = spec.prefix if spec is not None else ""
+        own = dict((("in", "in"), ("out", "out"), ("mix", "mix")))
+        own.update(dict(tensor_names or ()))
+        self._names = [{k: prefix + names.get(f"connect{q}", f"hc{q}") + "." + v for k, v in own.items()} for q in (1, 2)]
+        self.consts = [None, None]               # per sublayer: (in, out, mix) float32 on the device
+
+    @property
+    def has_ff(self) -> bool:
+        return not getattr(self.feed_forward, "absent", False)
+
+    def parts(self):
+        return (self.norm1, self.mixer, self.norm2, self.feed_forward) if self.has_ff else (self.norm1, self.mixer)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.parts())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [s for p in self.parts() for s in p.tensor_specs()]
+        if self.learned:
+            S = self.streams
+            for n in self._names[:2 if self.has_ff else 1]:
+                specs += [TensorSpec(n["in"], (S,), role="vector", init="norm"),
+                          TensorSpec(n["out"], (S,), role="vector", init="norm"),
+                          TensorSpec(n["mix"], (S, S), role="vector")]
+        return specs
+
+    def load(self, fetch: Fetch) -> None:
+        for p in self.parts():
+            p.load(fetch)
+        if self.learned:
+            for q, n in enumerate(self._names[:2 if self.has_ff else 1]):
+                self.consts[q] = (fetch(n["in"]).contiguous(), fetch(n["out"]).contiguous(), fetch(n["mix"]).contiguous())
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in self.parts())
+
+    def check_limits(self, dtype, max_context, page_size) -> None:
+        for p in self.parts():
+            p.check_limits(dtype, max_context, page_size)
+
+    def _const(self, q: int):
+        return self.consts[q] if self.learned else (None, None, None)
+
+    @staticmethod
+    def _groups(norm) -> int:
+        return int(getattr(norm, "groups", 1))
+
+    def _pending(self, h, pending):
+        """(y, mix, out) of what the block before left: its own kind, or an ordinary sum."""
+        from .base import StreamUpdate
+        if isinstance(pending, StreamUpdate):
+            return pending.y, pending.mix, pending.out
+        y = summed(pending)
+        if y is not None and self.streams != 1:
+            raise TypeError("an ordinary residual sum cannot be added to several streams")
+        return y, None, None
+
+    def settle(self, h: torch.Tensor, pending):
+        from .. import kernels
+        y, mix, out = self._pending(h, pending)
+        if y is not None:
+            kernels.streams_mix_norm(h, self.streams, y, mix, out, None, None, 0.0, 1, None)
+        return None
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, cache: Optional[CacheView],
+                state: Optional[torch.Tensor]):
+        from .. import kernels
+        from .base import StreamUpdate
+        S = self.streams
+        y, mix, out = self._pending(h, pending)
+        in1, out1, mix1 = self._const(0)
+        x1 = kernels.streams_mix_norm(h, S, y, mix, out, in1, self.norm1.weight, self.norm1.eps,
+                                      self._groups(self.norm1), ctx.dtype)
+        a = self.mixer.forward(x1, ctx, cache, state)
+        if not self.has_ff:
+            return StreamUpdate(a, mix1, out1)
+        in2, out2, mix2 = self._const(1)
+        x2 = kernels.streams_mix_norm(h, S, a, mix1, out1, in2, self.norm2.weight, self.norm2.eps,
+                                      self._groups(self.norm2), ctx.dtype)
+        return StreamUpdate(summed(self.feed_forward.forward(x2, ctx)), mix2, out2)

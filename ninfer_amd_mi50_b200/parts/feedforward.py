@@ -327,3 +327,140 @@ class SparseMoeSwiglu(FeedForward):
         if self.has_shared:
             shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
         return RoutedSum(y, plan, wts, shared, gate, x.dtype)
+
+
+@register_part("feed_forward", "dense_poly_norm")
+class DensePolyNorm(FeedForward):
+    """An ungated dense feed-forward ``W_down act(W_up x)`` whose activation is a polynomial of normed
+    powers: ``act(z) = a N(z) + b N(z^2) + c N(z^3) + e`` with the powers taken element by element,
+    ``N(v) = v / sqrt(mean(v^2) + eps)`` over a token's whole vector, and (a, b, c, e) one learned
+    tensor of four numbers.  The first product hands on its float32 sums; the means and the
+    polynomial are 32-bit in both modes."""
+
+    graph_safe = True
+    DEFAULT_NAMES = (("up", "up"), ("down", "down"), ("act", "act"))
+
+    def __init__(self, hidden_size: int, intermediate_size: int, eps: float, prefix: str, tensor_names=None):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.eps, self.prefix = float(eps), prefix
+        self.names = dict(self.DEFAULT_NAMES)
+        self.names.update(dict(tensor_names or ()))
+        self.w_up = self.w_down = self.coef = None
+
+    def _n(self, what: str) -> str:
+        return self.prefix + self.names[what]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        H, I = self.hidden_size, self.intermediate_size
+        return [TensorSpec(self._n("up"), (I, H)), TensorSpec(self._n("down"), (H, I)),
+                TensorSpec(self._n("act"), (4,), role="vector", init="norm")]
+
+    def load(self, fetch: Fetch) -> None:
+        self.w_up, self.w_down, self.coef = fetch(self._n("up")), fetch(self._n("down")), fetch(self._n("act"))
+
+    def weight_bytes(self) -> int:
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext):
+        z = kernels.linear(x, self.w_up, out_dtype=torch.float32)
+        return kernels.linear(kernels.poly_norm_act(z, self.coef, self.eps, x.dtype), self.w_down)
+
+
+@register_part("feed_forward", "table_routed_gelu")
+class TableRoutedGelu(FeedForward):
+    """A mixture of ungated experts ``W_down gelu(W_up x)`` (the exact, erf GELU; no biases) without a
+    router: a table ``[vocab, top]`` names each token id's experts, each weighing ``1 / top``.  An
+    optional shared expert of the same form runs for every token and is added, multiplied by
+    ``sigmoid(w_sg . x)``, one number a token.  The experts' rows are sorted by expert on the device
+    (the plan the routed experts of the other designs use), both products run over the sorted rows,
+    and the sum is left pending as a `RoutedSum`."""
+
+    graph_safe = True
+    DEFAULT_NAMES = (("table", "table"), ("up", "e{e}.up"), ("down", "e{e}.down"), ("shared_up", "shared.up"),
+                     ("shared_down", "shared.down"), ("shared_gate", "shared.sg"))
+
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int, vocab_size: int, moe_intermediate_size: int,
+                 shared_intermediate_size: int, prefix: str, tensor_names=None):
+        if not 1 <= top_k <= num_experts:
+            raise ValueError(f"top_k={top_k} must lie in [1, num_experts={num_experts}]")
+        kernels.check_router_sizes(num_experts, top_k)
+        self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
+        self.vocab_size = int(vocab_size)
+        self.moe_intermediate_size, self.shared_intermediate_size = int(moe_intermediate_size), int(shared_intermediate_size)
+        self.prefix = prefix
+        self.names = dict(self.DEFAULT_NAMES)
+        self.names.update(dict(tensor_names or ()))
+        self.table = self.w_up = self.w_down = self.ws_up = self.ws_down = self.w_sg = None
+        self._wts = {}
+
+    @property
+    def has_shared(self) -> bool:
+        return self.shared_intermediate_size > 0
+
+    def _n(self, what: str, e: int = 0) -> str:
+        return self.prefix + self.names[what].format(e=e)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        H, I, Is = self.hidden_size, self.moe_intermediate_size, self.shared_intermediate_size
+        specs = [TensorSpec(self._n("table"), (self.vocab_size, self.top_k), role="table",
+                            init=f"distinct:{self.num_experts}")]
+        for e in range(self.num_experts):
+            specs += [TensorSpec(self._n("up", e), (I, H)), TensorSpec(self._n("down", e), (H, I))]
+        if self.has_shared:
+            specs += [TensorSpec(self._n("shared_up"), (Is, H)), TensorSpec(self._n("shared_down"), (H, Is)),
+                      TensorSpec(self._n("shared_gate"), (1, H))]
+        return specs
+
+    def load(self, fetch: Fetch) -> None:
+        H, I, E = self.hidden_size, self.moe_intermediate_size, self.num_experts
+        self.table = fetch(self._n("table")).contiguous()
+        lo, hi = int(self.table.min()), int(self.table.max())
+        if lo < 0 or hi >= E:
+            raise ValueError(f"{self._n('table')}: entries {lo}..{hi} name experts outside 0..{E - 1}")
+        first = fetch(self._n("up", 0))
+        self.w_up = torch.empty((E, I, H), dtype=first.dtype, device=first.device)
+        self.w_down = torch.empty((E, H, I), dtype=first.dtype, device=first.device)
+        for e in range(E):
+            self.w_up[e].copy_(first if e == 0 else fetch(self._n("up", e)))
+            self.w_down[e].copy_(fetch(self._n("down", e)))
+        del first
+        if (self.w_up.is_cuda and self.w_up.dtype == torch.bfloat16 and kernels.can_pack(I, H)
+                and kernels.can_pack(H, I)):
+            self.w_up = kernels.pack_weights(self.w_up, swiglu=False)
+            self.w_down = kernels.pack_weights(self.w_down, swiglu=False)
+        if self.has_shared:
+            self.ws_up, self.ws_down = fetch(self._n("shared_up")), fetch(self._n("shared_down"))
+            self.w_sg = fetch(self._n("shared_gate"))
+
+    def _expert_total_bytes(self) -> int:
+        if isinstance(self.w_up, kernels.PackedWeights):
+            return self.w_up.nbytes() + self.w_down.nbytes()
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def expert_bytes(self) -> int:
+        return self._expert_total_bytes() // self.num_experts
+
+    def weight_bytes(self) -> int:
+        n = self._expert_total_bytes() + self.table.numel() * 4
+        if self.has_shared:
+            n += (self.ws_up.numel() + self.ws_down.numel() + self.w_sg.numel()) * self.ws_down.element_size()
+        return n
+
+    def _weights(self, T: int, device) -> torch.Tensor:
+        """float32 [T, top] of 1 / top, kept by row count (a step's graph may name it again)."""
+        key = (T, str(device))
+        if key not in self._wts:
+            self._wts[key] = torch.full((T, self.top_k), 1.0 / self.top_k, dtype=torch.float32, device=device)
+        return self._wts[key]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext):
+        E, k = self.num_experts, self.top_k
+        idx = kernels.table_route(self.table, ctx.token_ids, E)
+        plan = kernels.moe_plan(idx, E)
+        a = kernels.gelu_erf_(kernels.moe_rows_gemm(x, self.w_up, plan, k, from_tokens=True))
+        y = kernels.moe_rows_gemm(a, self.w_down, plan, k, from_tokens=False)
+        shared = gate = None
+        if self.has_shared:
+            shared = kernels.linear(kernels.gelu_erf_(kernels.linear(x, self.ws_up)), self.ws_down)
+            gate = kernels.linear(x, self.w_sg, out_dtype=torch.float32)          # [T, 1] logits
+        return RoutedSum(y, plan, self._weights(x.shape[0], x.device), shared, gate, x.dtype)

@@ -17,7 +17,7 @@ import torch
 from .. import kernels
 from ..config.model_config import LayerCall, ModelPlan
 from ..registry import build_part, part_class
-from .base import CacheSpec, CacheView, Fetch, RoutedSum, StateSpec, StepContext, TensorSpec, summed
+from .base import CacheSpec, CacheView, Fetch, RoutedSum, StateSpec, StepContext, StreamUpdate, TensorSpec, summed
 
 
 class DecoderModel:
@@ -33,9 +33,15 @@ class DecoderModel:
             block_cls = part_class("block", spec.arrangement)
             # an arrangement with tensors of its own (a layer scale, say) is told the layer's names
             extra = {"spec": spec} if getattr(block_cls, "wants_spec", False) else {}
+            extra.update(dict(spec.arrangement_params))
             self.blocks.append(block_cls(norm1, mixer, norm2, ffn, **extra))
         self.embedding_extras = [build_part("embedding", e) for e in plan.embedding_extras]
         self.final_norm = build_part("norm", plan.final_norm, prefix=plan.final_norm_name)
+        self.streams = int(plan.streams)
+        if not 1 <= self.streams <= kernels.MAX_STREAMS:
+            raise ValueError(f"{self.streams} residual streams a token; the kernels take 1 to {kernels.MAX_STREAMS}")
+        if self.streams > 1 and plan.embedding_extras:
+            raise ValueError("rows added to the embedding and several residual streams do not go together")
         self.order: List[LayerCall] = list(plan.order)
         vectors = dict(plan.stream_vectors)
         for call in self.order:
@@ -91,8 +97,9 @@ class DecoderModel:
                 raise ValueError(f"{what} slot {slot} is shared by layers that keep different things")
             named.add(slot)
             specs[slot] = spec
-        for i, b in enumerate(self.blocks):          # a layer the order never names keeps its own slot
-            if i not in named:
+        called = {call.layer for call in self.order}
+        for i, b in enumerate(self.blocks):          # a layer the order never runs keeps its own slot;
+            if i not in named and i not in called:   # one that only ever reads another's slot keeps none
                 specs[i] = spec_of(b)
         return specs
 
@@ -126,8 +133,11 @@ class DecoderModel:
                 cache_view: Callable[[int, bool], Optional[CacheView]],
                 state_of: Callable[[int], Optional[torch.Tensor]]) -> torch.Tensor:
         """Run every row of the step; return float32 logits [R, vocab] for ctx.logit_rows."""
-        h = torch.empty((ctx.T, self.hidden_size), dtype=torch.float32, device=ctx.device)
-        kernels.embed_rows(self.embedding, ctx.token_ids, h)
+        h = torch.empty((ctx.T, self.hidden_size * self.streams), dtype=torch.float32, device=ctx.device)
+        if self.streams == 1:
+            kernels.embed_rows(self.embedding, ctx.token_ids, h)
+        else:
+            kernels.embed_copies(self.embedding, ctx.token_ids, h, self.streams)
         for i, e in enumerate(self.embedding_extras):
             e.add(h, ctx, state_of(self.extra_state_slot0 + i))
         pending = None
@@ -138,14 +148,19 @@ class DecoderModel:
             pending = self.blocks[call.layer].forward(
                 h, pending, ctx, cache_view(call.cache, call.append), state_of(call.state_slot()))
             if self.probe is not None:
+                pending = self.blocks[call.layer].settle(h, pending)
                 self.probe(run, h)
         R = ctx.logit_rows.numel()
         if R == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=ctx.device)
-        if not self.final_norm.takes_unsummed or not isinstance(pending, (torch.Tensor, RoutedSum, type(None))):
+        if isinstance(pending, StreamUpdate) and getattr(self.final_norm, "takes_stream_update", False):
+            pass                                     # the norm applies the update in its own pass over the rows
+        elif not self.final_norm.takes_unsummed or not isinstance(pending, (torch.Tensor, RoutedSum, type(None))):
             pending = summed(pending)
         x = self.final_norm.add_norm_rows(h, pending, ctx.logit_rows, ctx.dtype)
         logits = kernels.linear(x, self.head, out_dtype=torch.float32)
         if self.plan.logit_scale != 1.0:
             logits.mul_(self.plan.logit_scale)
+        if self.plan.logit_softcap > 0.0:
+            kernels.softcap(logits, self.plan.logit_softcap)
         return logits

@@ -125,3 +125,51 @@ class LayerNorm(Norm):
         routed = self._routed(delta, out_dtype)
         kernels.add_layernorm(h, None if routed else summed(delta), rows, self.weight, self.eps, out, routed=routed)
         return out
+
+
+@register_part("norm", "group_rms_norm")
+class GroupRmsNorm(Norm):
+    """RMS norm in groups: the row is cut into `groups` equal consecutive parts, each divided by its
+    own ``sqrt(mean(part^2) + eps)``, and the whole multiplied by the weight.  One group is the usual
+    RMS norm.  Fused with the residual sum; the stream may hold several copies a token (`h` is then
+    ``[T, streams * size]``), in which case the norm reads their plain sum and a pending
+    `StreamUpdate` is applied in the same pass.  Sum, means and products are 32-bit in both modes."""
+
+    graph_safe = True
+    takes_unsummed = False
+    takes_stream_update = True
+
+    def __init__(self, size: int, eps: float, prefix: str, groups: int = 1, weight_name: str = "weight"):
+        self.size, self.eps, self.prefix = int(size), float(eps), prefix
+        self.groups, self.weight_name = int(groups), weight_name
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"a row of {self.size} does not split into {self.groups} equal groups")
+        self.weight: Optional[torch.Tensor] = None
+
+    def _name(self) -> str:
+        return self.prefix + self.weight_name if self.weight_name else self.prefix.rstrip(".")
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self._name(), (self.size,), role="vector", init="norm")]
+
+    def load(self, fetch: Fetch) -> None:
+        self.weight = fetch(self._name())
+
+    def weight_bytes(self) -> int:
+        return self.size * 4
+
+    def _apply(self, h, delta, rows, out_dtype):
+        from .base import StreamUpdate
+        S = h.shape[1] // self.size
+        if isinstance(delta, StreamUpdate):
+            y, mix, out = delta.y, delta.mix, delta.out
+        else:
+            y, mix, out = summed(delta), None, None
+        return kernels.streams_mix_norm(h, S, y, mix, out, None, self.weight, self.eps, self.groups, out_dtype,
+                                        rows=rows)
+
+    def add_norm(self, h, delta, out_dtype):
+        return self._apply(h, delta, None, out_dtype)
+
+    def add_norm_rows(self, h, delta, rows, out_dtype):
+        return self._apply(h, delta, rows, out_dtype)

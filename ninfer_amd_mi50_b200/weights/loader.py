@@ -115,6 +115,12 @@ class RandomSource:
         spec = self.specs[name]
         device = torch.device(device) if device is not None else self.gen_device
         if spec.role == "table":
+            if spec.init.startswith("distinct:"):
+                # rows of different numbers below n: (a multiple of the row's number + the column) mod n
+                n = int(spec.init.split(":")[1])
+                r = torch.arange(spec.shape[0], dtype=torch.int64, device=device)[:, None]
+                j = torch.arange(spec.shape[1], dtype=torch.int64, device=device)[None, :]
+                return ((r * 2654435761 + (self.seed % 1000003)) % n + j).remainder(n).to(torch.int32)
             return torch.zeros(spec.shape, dtype=torch.int32, device=device)
         out = torch.empty(spec.shape, dtype=dtype, device=device)
         return counter_rng.fill(out, counter_rng.tensor_keys(self.seed, name), spec.init)
