@@ -43,20 +43,17 @@ __global__ void gelu_erf_kernel(T* __restrict__ x, size_t n) {
   }
 }
 
-// idx[t, j] = table[ids[t], j]: the experts of a token stand in a table by its id.  An entry outside
-// [0, E) (or an id outside the table) becomes expert 0 and is counted in *bad.
+// idx[t, j] = table[ids[t], j]: the experts of a token stand in a table by its id.  The loader has
+// checked that every entry names an expert and the step that every id lies in the table; an entry
+// that does not is read as expert 0 rather than followed.
 __global__ void table_route_kernel(const int* __restrict__ table, const int* __restrict__ ids, int* __restrict__ idx,
-                                   int T, int k, int rows, int E, int* __restrict__ bad) {
+                                   int T, int k, int rows, int E) {
   chain_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * k) return;
   const int id = ids[i / k];
-  int e = (id >= 0 && id < rows) ? table[(size_t)id * k + i % k] : -1;
-  if (e < 0 || e >= E) {
-    atomicAdd(bad, 1);
-    e = 0;
-  }
-  idx[i] = e;
+  const int e = (id >= 0 && id < rows) ? table[(size_t)id * k + i % k] : 0;
+  idx[i] = (e >= 0 && e < E) ? e : 0;
 }
 
 // out[r, i] = T(y[r, i] + bias[i]): the bias of a projection whose float32 sums were kept
@@ -67,8 +64,6 @@ __global__ void add_bias_rows_kernel(const float* __restrict__ y, const float* _
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < total) out[i] = from_float<T>(y[i] + bias[i % n]);
 }
-
-static int* g_route_bad = nullptr;
 
 }  // namespace nf
 
@@ -102,23 +97,8 @@ extern "C" int nf_table_route(const int* table, const int* ids, int* idx, int T,
                               cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && k > 0 && rows > 0 && E > 0, "table_route: bad sizes T=%d k=%d rows=%d E=%d", T, k, rows, E);
-  if (!g_route_bad) {
-    if (cudaMalloc(&g_route_bad, sizeof(int)) != cudaSuccess || cudaMemset(g_route_bad, 0, sizeof(int)) != cudaSuccess) {
-      set_error("table_route: no memory for the status word");
-      return 1;
-    }
-  }
-  launch_chained(table_route_kernel, dim3((T * k + 127) / 128), dim3(128), 0, stream, table, ids, idx, T, k, rows, E, g_route_bad);
+  launch_chained(table_route_kernel, dim3((T * k + 127) / 128), dim3(128), 0, stream, table, ids, idx, T, k, rows, E);
   return check_launch("table_route");
-}
-
-// Entries that were outside their table or named no expert since the last call; reads and resets.
-extern "C" int nf_table_route_status() {
-  if (!g_route_bad) return 0;
-  int v = 0;
-  if (cudaMemcpy(&v, g_route_bad, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (v) cudaMemset(g_route_bad, 0, sizeof(int));
-  return v;
 }
 
 extern "C" int nf_add_bias_rows(const float* y, const float* bias, void* out, int R, int n, int dtype, cudaStream_t stream) {

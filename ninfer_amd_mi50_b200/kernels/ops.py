@@ -325,14 +325,11 @@ def tensor_core_status() -> int:
 def index_status() -> int:
     """0, or what a kernel that follows device-side indices found outside its operands since the
     last call (it skips such an access): 201-203 the streaming product (group, row range, row
-    index), 300 + token + 1 the combine, 400 an expert table's entry that names no expert, 100000 + row + 1 a decode-attention row whose position
+    index), 300 + token + 1 the combine, 100000 + row + 1 a decode-attention row whose position
     lay beyond the key blocks its call allowed for.  Synchronises the device."""
     lib = _lib.load()
     sk, cb = int(lib.nf_skinny_index_status()), int(lib.nf_combine_index_status())
     da = int(lib.nf_decode_attention_status())
-    tr = int(lib.nf_table_route_status())
-    if tr:
-        return 400
     return 200 + sk if sk else (300 + cb if cb else (100000 + da if da else 0))
 
 
