@@ -3,6 +3,7 @@ every kernel of one step timed by name against its roofline.
 
     python bench.py --config vekasun
     python bench.py --config difavik
+    python bench.py --config fetezen
 
 For each named size a Vekasun model (latent attention and state-space mixers alternating, routed
 experts scored by a sigmoid and weighted on their input) and a Qwen2-MoE model of the same width,
@@ -64,6 +65,26 @@ def difavik_config(s: dict) -> dict:
                        for k in kinds]}
 
 
+# the Fetezen design at the same sizes: four residual streams, norms in four groups, as many key heads as query
+# heads (as the Qwen2-MoE model beside it), chunks of 1,536 positions (a prompt of 2,048 holds one whole chunk and a
+# part of the next; a request at 2,048 decodes a third into its chunk), every second layer reading the keys of the
+# layer before it, one dense layer as wide as a token's chosen experts together, one shared expert
+STREAMS, NORM_GROUPS, CHUNK = 4, 4, 1536
+
+
+def fetezen_config(s: dict) -> dict:
+    H = s["heads"]
+    att = lambda src: dict({"heads": H, "kv_heads": H, "dim": HEAD_DIM, "vdim": HEAD_DIM, "scale": HEAD_DIM ** -0.5,
+                            "rot": {"base": 10000.0, "dims": HEAD_DIM}, "mask": {"size": CHUNK}},
+                           **({} if src is None else {"kv_from": src}))
+    moe = lambda shared: dict({"kind": "moe", "expert": {"ff": s["ff"]}, "router": {"experts": s["experts"], "top": s["top"]}},
+                              **({"shared": {"ff": s["ff"]}} if shared else {}))
+    mlps = [{"kind": "dense", "ff": s["top"] * s["ff"]}, moe(False), moe(True), moe(False)]
+    return {"architecture": "Fetezen", "vocab": VOCAB, "width": s["width"], "streams": STREAMS, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6, "groups": NORM_GROUPS},
+            "layers": [{"type": "attention", "mixer": att(src), "mlp": mlp} for src, mlp in zip((None, 0, None, 2), mlps)]}
+
+
 def qwen2_moe_config(s: dict) -> dict:
     return {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "num_hidden_layers": LAYERS,
             "hidden_size": s["width"], "num_attention_heads": s["heads"], "num_key_value_heads": s["heads"],
@@ -112,12 +133,23 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
     state = s["ssm_heads"] * SSM_HEAD_DIM * N * 4
     D = HEAD_DIM
 
-    def phase(T, pairs, rows_ctx, nseg, pairs_w=0.0, rows_w=0):
+    def phase(T, pairs, rows_ctx, nseg, pairs_w=0.0, rows_w=0, pairs_c=0.0, rows_c=0):
         # pairs: sum over rows of the keys each sees; rows_ctx: cache tokens that must be read once;
-        # pairs_w, rows_w: the same under the Difavik comparison's window
+        # pairs_w, rows_w: the same under the Difavik comparison's window; pairs_c, rows_c: under Fetezen's chunks
         la = lambda Dk, Dv: (T * H * (2 * Dk + Dv) * 2 + T * H * Dv * 4 + 2 * nseg * H * Dk * Dv * 4, 4.0 * T * H * Dk * Dv)
         windowed = (rows_w * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs_w)
+        chunked = lambda rows, prs: (rows * H * 2 * D * 2 + 2 * T * H * D * 2, (4.0 * H * D + 2.0 * H * H) * prs)
         return {
+            # Fetezen: keys and values of the rows' chunks once, queries in and outputs out; both products and the
+            # mixing of the heads' scores
+            "nf_talking_attention": chunked(rows_c, pairs_c),
+            "nf_talking_attention_mma": chunked(rows_c, pairs_c),
+            "nf_talking_attention_split": chunked(rows_c, pairs_c),
+            "nf_streams_mix_norm": (T * W * (8 * STREAMS + 2 + 2), 0.0),
+            "nf_head_norm_rope_append": (T * 3 * H * D * (4 + 2), 0.0),
+            "nf_add_bias_rows": (T * W * (4 + 2), 0.0),
+            "nf_poly_norm_act": (T * s["top"] * s["ff"] * (4 + 2), 0.0),
+            "nf_embed_copies": (T * W * (2 + 4 * STREAMS), 0.0),
             "nf_prefill_attention_biased": windowed,
             "nf_paged_attention_generic": windowed,
             # two shapes share the kernel (lightning 128 x 128, retention 64 x 128): the mean of the two
@@ -149,9 +181,11 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
         }
 
     seen = lambda p: min(p + 1, WINDOW) + max(0, min(KEEP_FIRST, p + 1 - WINDOW))       # keys position p sees
-    return {"prefill": phase(prompt, prompt * (prompt + 1) / 2, prompt, 1, float(sum(seen(p) for p in range(prompt))), prompt),
+    in_chunk = lambda p: p % CHUNK + 1                                                  # keys position p sees in its chunk
+    return {"prefill": phase(prompt, prompt * (prompt + 1) / 2, prompt, 1, float(sum(seen(p) for p in range(prompt))), prompt,
+                             float(sum(in_chunk(p) for p in range(prompt))), prompt),
             "decode": phase(batch, batch * (context + 1), batch * (context + 1), batch, float(batch * seen(context)),
-                            batch * seen(context))}
+                            batch * seen(context), float(batch * in_chunk(context)), batch * in_chunk(context))}
 
 
 def measure(config: dict, prompt: int, batch: int, context: int, steps: int, warmup: int) -> dict:
@@ -228,7 +262,7 @@ def measure(config: dict, prompt: int, batch: int, context: int, steps: int, war
     return out
 
 
-DESIGNS = {"vekasun": vekasun_config, "difavik": difavik_config}
+DESIGNS = {"vekasun": vekasun_config, "difavik": difavik_config, "fetezen": fetezen_config}
 
 
 def run_comparison(sizes, peaks: dict, prompt: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32,
