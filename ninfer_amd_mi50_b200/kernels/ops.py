@@ -1472,6 +1472,11 @@ def head_norm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], q_no
     return q
 
 
+TALKING_TILE_ROWS = 32      # rows a tile of the tensor-core kernel
+TALKING_KEY_BLOCK = 32      # keys a block of that kernel
+TALKING_SPLIT_CTAS = 296    # steps of single rows: their keys are cut into runs until about this many CTAs run
+
+
 def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: torch.Tensor,
                       block_table: torch.Tensor, page_size: int, ctx, chunk: int, scale: float,
                       talk: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
@@ -1481,6 +1486,34 @@ def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: t
     _chk(q, "q"); _chk(pages, "pages", q.dtype)
     T = q.shape[0]
     out = torch.empty((T, H * Dv), dtype=q.dtype, device=q.device)
+    if T == 0:
+        return out
+    per_cta = 0
+    if q.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic":
+        per_cta = _lib.load().nf_talking_attention_mma_heads_per_cta(c_int(H), c_int(G), c_int(D), c_int(Dv))
+    if per_cta > 0:
+        # tensor cores: tiles of 16 rows with all heads, the heads dealt out over a cluster's CTAs
+        single = getattr(ctx, "all_single", False) or getattr(ctx, "seg_len_host", None) is None
+        nsplit, per_split, ws_o, ws_ml = 1, 1, None, None
+        if single:
+            # one row a segment: the kernel numbers the tiles itself, and a row's keys (from its chunk's
+            # start) are cut into runs so that the device is filled
+            tiles, n_tiles = None, ctx.S
+            span = max(1, min(chunk, int(ctx.max_context)) if chunk > 0 else int(ctx.max_context))
+            n_blocks = (span + TALKING_KEY_BLOCK - 1) // TALKING_KEY_BLOCK + (1 if chunk % TALKING_KEY_BLOCK else 0)
+            nsplit = min(n_blocks, max(1, TALKING_SPLIT_CTAS // (n_tiles * (H // per_cta))))
+            per_split = max(2, (n_blocks + nsplit - 1) // nsplit)
+            nsplit = (n_blocks + per_split - 1) // per_split
+            if nsplit > 1:
+                ws_o = torch.empty((T * H, nsplit, Dv), dtype=torch.float32, device=q.device)
+                ws_ml = torch.empty((T * H, nsplit, 2), dtype=torch.float32, device=q.device)
+        else:
+            tiles, n_tiles = ctx.query_tiles(TALKING_TILE_ROWS)
+        _lib.call("nf_talking_attention_mma", _p(q), _p(pages), _p(block_table), c_int(block_table.shape[1]),
+                  _p(ctx.positions), _p(ctx.seg_row0), _p(tiles), c_int(n_tiles), _p(talk), _p(sink), _p(out),
+                  _p(ws_o), _p(ws_ml), c_int(T), c_int(H), c_int(G), c_int(D), c_int(Dv), c_int(page_size),
+                  c_int(pages.shape[0]), c_int(chunk), c_float(scale), c_int(nsplit), c_int(per_split), _stream())
+        return out
     _lib.call("nf_talking_attention", _p(q), _p(pages), _p(block_table), c_int(block_table.shape[1]),
               _p(ctx.positions), _p(ctx.row_seg), None, _p(talk), _p(sink), _p(out), c_int(T), c_int(H), c_int(G),
               c_int(D), c_int(Dv), c_int(page_size), c_int(pages.shape[0]), c_int(chunk), c_float(scale),
