@@ -64,6 +64,20 @@ __device__ __forceinline__ float4 tm_ld_cluster4(unsigned addr) {
   asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
+// a row of the mixing weights [HC] from shared memory (16 bytes a read where the rows are so aligned)
+template <int HC>
+__device__ __forceinline__ void tm_talk_row(const float* p, float* w) {
+  if constexpr (HC % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < HC / 4; ++i) {
+      const float4 v = *reinterpret_cast<const float4*>(p + i * 4);
+      w[i * 4] = v.x; w[i * 4 + 1] = v.y; w[i * 4 + 2] = v.z; w[i * 4 + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < HC; ++i) w[i] = p[i];
+  }
+}
 __device__ __forceinline__ void tm_cp16(unsigned dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -100,7 +114,8 @@ __host__ __device__ inline TmLayout tm_layout(int H, int G, int D, int Dv, int H
 }  // namespace
 
 // tiles: int32 [n_tiles, 2] of (segment, first row); null when every segment brings one row (tile i is
-// segment i).  ws_o float32 [T * H, nsplit, Dv], ws_ml float32 [T * H, nsplit, 2]: used when nsplit > 1.
+// segment i).  ws_o float32 [T * H, nsplit, Dv], ws_ml float32 [T * H, nsplit, 2], or both null: with them
+// the CTAs of run `blockIdx.y` write partial sums there, which the merge kernel adds up with the sink.
 template <int HC, int NU>      // heads a CTA; (head, 16 columns) units of the second product a warp
 __global__ void __launch_bounds__(kTmThreads, 1)
 talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
@@ -166,8 +181,9 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     j_hi = max(j_hi, row_pos[r]);
   }
   const int b_first = j_lo / kTmKeys;
-  const int b_begin = nsplit > 1 ? b_first + split * blocks_per_split : b_first;
-  const int b_end = nsplit > 1 ? min(j_hi / kTmKeys + 1, b_begin + blocks_per_split) : j_hi / kTmKeys + 1;
+  const bool partial = ws_o != nullptr;                // runs of blocks whose sums a second kernel merges
+  const int b_begin = partial ? b_first + split * blocks_per_split : b_first;
+  const int b_end = partial ? min(j_hi / kTmKeys + 1, b_begin + blocks_per_split) : j_hi / kTmKeys + 1;
   const int* bt = block_table + (size_t)seg * bt_width;
 
   // eight threads a key row: the row's page is looked up once, then 16-byte copies at a stride of eight
@@ -195,7 +211,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   // raw score is read once a CTA, and a warp's reads of a row are 128 consecutive bytes)
   const int mi = tid >> 3, kq = tid & 7;
   const int my_pos = row_pos[mi], my_lo = row_lo[mi];
-  const bool with_sink = sink != nullptr && nsplit == 1;
+  const bool with_sink = sink != nullptr && !partial;
   float m_run[HC], l_run[HC];
 #pragma unroll
   for (int h = 0; h < HC; ++h) {
@@ -272,40 +288,53 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       for (int h = 0; h < HC; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
       const unsigned s_ofs = (unsigned)((((size_t)buf * HC * kTmRows + mi) * kTmSP + kq * 4) * sizeof(float));
       // own scores first, then the other CTAs' in a round that starts behind this CTA's rank, so that no
-      // CTA's shared memory is asked by all the others at once
+      // CTA's shared memory is asked by all the others at once; the reads of the next CTA's scores are
+      // in flight while this one's are mixed
+      float4 sv[HC];
+      if (C > 1) {
+        const unsigned src = tm_mapa(tm_smem(Ss), (unsigned)(rank + 1 < C ? rank + 1 : 0)) + s_ofs;
+#pragma unroll
+        for (int gl = 0; gl < HC; ++gl) sv[gl] = tm_ld_cluster4(src + (unsigned)(gl * kTmRows * kTmSP * sizeof(float)));
+      }
       {
         const float* src = Ss + s_ofs / sizeof(float);
         const float* tk = talk_s + (size_t)rank * HC * HC;
 #pragma unroll
         for (int gl = 0; gl < HC; ++gl) {
-          const float4 sv = *reinterpret_cast<const float4*>(src + (size_t)gl * kTmRows * kTmSP);
+          const float4 lv = *reinterpret_cast<const float4*>(src + (size_t)gl * kTmRows * kTmSP);
+          float w[HC];
+          tm_talk_row<HC>(tk + gl * HC, w);
 #pragma unroll
           for (int h = 0; h < HC; ++h) {
-            const float w = tk[gl * HC + h];
-            acc[h][0] = fmaf(w, sv.x, acc[h][0]);
-            acc[h][1] = fmaf(w, sv.y, acc[h][1]);
-            acc[h][2] = fmaf(w, sv.z, acc[h][2]);
-            acc[h][3] = fmaf(w, sv.w, acc[h][3]);
+            acc[h][0] = fmaf(w[h], lv.x, acc[h][0]);
+            acc[h][1] = fmaf(w[h], lv.y, acc[h][1]);
+            acc[h][2] = fmaf(w[h], lv.z, acc[h][2]);
+            acc[h][3] = fmaf(w[h], lv.w, acc[h][3]);
           }
         }
       }
       for (int step = 1; step < C; ++step) {
         const int c = rank + step < C ? rank + step : rank + step - C;
-        const unsigned src = tm_mapa(tm_smem(Ss), (unsigned)c) + s_ofs;
         const float* tk = talk_s + (size_t)c * HC * HC;
-        float4 sv[HC];
+        float4 cur[HC];
 #pragma unroll
-        for (int gl = 0; gl < HC; ++gl)
-          sv[gl] = tm_ld_cluster4(src + (unsigned)(gl * kTmRows * kTmSP * sizeof(float)));
+        for (int gl = 0; gl < HC; ++gl) cur[gl] = sv[gl];
+        if (step + 1 < C) {
+          const int cn = c + 1 < C ? c + 1 : 0;
+          const unsigned src = tm_mapa(tm_smem(Ss), (unsigned)cn) + s_ofs;
+#pragma unroll
+          for (int gl = 0; gl < HC; ++gl) sv[gl] = tm_ld_cluster4(src + (unsigned)(gl * kTmRows * kTmSP * sizeof(float)));
+        }
 #pragma unroll
         for (int gl = 0; gl < HC; ++gl) {
+          float w[HC];
+          tm_talk_row<HC>(tk + gl * HC, w);
 #pragma unroll
           for (int h = 0; h < HC; ++h) {
-            const float w = tk[gl * HC + h];
-            acc[h][0] = fmaf(w, sv[gl].x, acc[h][0]);
-            acc[h][1] = fmaf(w, sv[gl].y, acc[h][1]);
-            acc[h][2] = fmaf(w, sv[gl].z, acc[h][2]);
-            acc[h][3] = fmaf(w, sv[gl].w, acc[h][3]);
+            acc[h][0] = fmaf(w[h], cur[gl].x, acc[h][0]);
+            acc[h][1] = fmaf(w[h], cur[gl].y, acc[h][1]);
+            acc[h][2] = fmaf(w[h], cur[gl].z, acc[h][2]);
+            acc[h][3] = fmaf(w[h], cur[gl].w, acc[h][3]);
           }
         }
       }
@@ -392,7 +421,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
 #pragma unroll
     for (int h = 0; h < HC; ++h) {
       l_s[h * kTmRows + mi] = l_run[h];
-      if (nsplit > 1 && mi < nrows) {
+      if (partial && mi < nrows) {
         const size_t slot = ((size_t)(row0 + mi) * H + h0 + h) * nsplit + split;
         ws_ml[slot * 2] = m_run[h];
         ws_ml[slot * 2 + 1] = l_run[h];
@@ -411,7 +440,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       for (int half = 0; half < 2; ++half) {
         const int r = mt * 16 + half * 8 + (lane >> 2);
         if (r >= nrows) continue;
-        if (nsplit > 1) {
+        if (partial) {
           float* dst = ws_o + (((size_t)(row0 + r) * H + h0 + h) * nsplit + split) * Dv + col;
 #pragma unroll
           for (int nt = 0; nt < 2; ++nt)
@@ -499,7 +528,8 @@ extern "C" int nf_talking_attention_mma(const void* q, const void* pages, const 
   const int hc = tm_heads_per_cta(H, G, D, Dv);
   NF_REQUIRE(hc > 0, "talking attention (tensor cores): sizes H=%d G=%d D=%d Dv=%d do not fit", H, G, D, Dv);
   NF_REQUIRE(chunk >= 0 && page_size > 0 && nsplit >= 1 && blocks_per_split >= 1, "talking attention: bad chunk, page size or split");
-  NF_REQUIRE(nsplit == 1 || (tiles == nullptr && ws_o && ws_ml), "talking attention: only steps of single rows are split");
+  NF_REQUIRE((ws_o == nullptr) == (ws_ml == nullptr), "talking attention: one workspace without the other");
+  NF_REQUIRE(ws_o ? tiles == nullptr : nsplit == 1, "talking attention: only steps of single rows are split");
   const int C = H / hc;
   const size_t smem = tm_layout(H, G, D, Dv, hc).total;
   const dim3 grid(n_tiles * C, nsplit);
@@ -531,7 +561,7 @@ extern "C" int nf_talking_attention_mma(const void* q, const void* pages, const 
   }
 #undef NF_TM_HC
 #undef NF_TM
-  if (nsplit > 1)
+  if (ws_o)
     launch_chained(talking_attention_merge_kernel, dim3(T * H), dim3(64), 0, stream, (const float*)ws_o,
                    (const float*)ws_ml, sink, (__nv_bfloat16*)out, H, Dv, nsplit);
   return check_launch("talking_attention_mma");

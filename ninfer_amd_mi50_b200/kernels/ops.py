@@ -1475,6 +1475,7 @@ def head_norm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], q_no
 TALKING_TILE_ROWS = 32      # rows a tile of the tensor-core kernel
 TALKING_KEY_BLOCK = 32      # keys a block of that kernel
 TALKING_SPLIT_CTAS = 296    # steps of single rows: their keys are cut into runs until about this many CTAs run
+TALKING_SPLIT_BLOCKS = 16   # ... without chunks, into runs of this many blocks
 
 
 def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: torch.Tensor,
@@ -1492,23 +1493,30 @@ def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: t
     if q.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic":
         per_cta = _lib.load().nf_talking_attention_mma_heads_per_cta(c_int(H), c_int(G), c_int(D), c_int(Dv))
     if per_cta > 0:
-        # tensor cores: tiles of 16 rows with all heads, the heads dealt out over a cluster's CTAs
+        # tensor cores: tiles of 32 rows with all heads, the heads dealt out over a cluster's CTAs
         single = getattr(ctx, "all_single", False) or getattr(ctx, "seg_len_host", None) is None
         nsplit, per_split, ws_o, ws_ml = 1, 1, None, None
         if single:
             # one row a segment: the kernel numbers the tiles itself, and a row's keys (from its chunk's
-            # start) are cut into runs so that the device is filled
+            # start) are cut into runs so that the device is filled.  A run's length depends on the number
+            # of rows and on the chunk, not on the step's longest context (which only bounds the number of
+            # runs launched): a captured step, which knows a bound only, rounds as a host-driven one does.
             tiles, n_tiles = None, ctx.S
+            block = TALKING_KEY_BLOCK
+            want = max(1, TALKING_SPLIT_CTAS // (n_tiles * (H // per_cta)))
+            if chunk > 0:
+                chunk_blocks = (chunk + block - 1) // block + (1 if chunk % block else 0)
+                per_split = max(2, (chunk_blocks + want - 1) // want)
+            else:
+                per_split = TALKING_SPLIT_BLOCKS
             span = max(1, min(chunk, int(ctx.max_context)) if chunk > 0 else int(ctx.max_context))
-            n_blocks = (span + TALKING_KEY_BLOCK - 1) // TALKING_KEY_BLOCK + (1 if chunk % TALKING_KEY_BLOCK else 0)
-            nsplit = min(n_blocks, max(1, TALKING_SPLIT_CTAS // (n_tiles * (H // per_cta))))
-            per_split = max(2, (n_blocks + nsplit - 1) // nsplit)
+            n_blocks = (span + block - 1) // block + (1 if chunk % block else 0)
             nsplit = (n_blocks + per_split - 1) // per_split
-            if nsplit > 1:
-                ws_o = torch.empty((T * H, nsplit, Dv), dtype=torch.float32, device=q.device)
-                ws_ml = torch.empty((T * H, nsplit, 2), dtype=torch.float32, device=q.device)
+            # partial sums and the merge also when one run is enough: the same arithmetic at every context
+            ws_o = torch.empty((T * H, nsplit, Dv), dtype=torch.float32, device=q.device)
+            ws_ml = torch.empty((T * H, nsplit, 2), dtype=torch.float32, device=q.device)
         else:
-            tiles, n_tiles = ctx.query_tiles(TALKING_TILE_ROWS)
+            tiles, n_tiles = ctx.chunked_query_tiles(TALKING_TILE_ROWS, chunk)
         _lib.call("nf_talking_attention_mma", _p(q), _p(pages), _p(block_table), c_int(block_table.shape[1]),
                   _p(ctx.positions), _p(ctx.seg_row0), _p(tiles), c_int(n_tiles), _p(talk), _p(sink), _p(out),
                   _p(ws_o), _p(ws_ml), c_int(T), c_int(H), c_int(G), c_int(D), c_int(Dv), c_int(page_size),

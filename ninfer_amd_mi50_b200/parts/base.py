@@ -160,6 +160,32 @@ class StepContext:
         return t, n_tiles
 
 
+    def chunked_query_tiles(self, rows_per_tile: int, chunk: int) -> Tuple[torch.Tensor, int]:
+        """`query_tiles` for attention over chunks of `chunk` positions (0: plain causal), the tiles
+        that read the most keys first: a tile's keys run from the start of its first row's chunk to
+        its last row, and the device hands CTAs to SMs as they fall free, so the light tiles fill
+        the end.  Built on the host; not available in graph mode."""
+        key = ("chunked_query_tiles", rows_per_tile, chunk)
+        if key in self._tiles:
+            return self._tiles[key]
+        if self.seg_len_host is None:
+            raise RuntimeError("chunked_query_tiles needs host segment lengths (not in graph mode)")
+        found = []
+        pos0 = self.seg_pos0_host or [0] * len(self.seg_len_host)
+        row = 0
+        for s, n in enumerate(self.seg_len_host):
+            for r in range(0, n, rows_per_tile):
+                first, last = pos0[s] + r, pos0[s] + min(n, r + rows_per_tile) - 1
+                start = (first // chunk) * chunk if chunk > 0 else 0
+                found.append((-(last - start), s, row + r))
+            row += n
+        found.sort()
+        flat: List[int] = [v for _, s, r in found for v in (s, r)]
+        n_tiles = len(flat) // 2
+        t = torch.tensor(flat, dtype=torch.int32).reshape(n_tiles, 2).to(self.device)
+        self._tiles[key] = (t, n_tiles)
+        return t, n_tiles
+
     def pair_tiles(self, heads: int, pairs_per_tile: int) -> Tuple[torch.Tensor, int]:
         """Tiles over the (row, head) pairs of every segment, `pairs_per_tile` consecutive pairs of
         one segment each (pair = row within the segment * heads + head).  Returns (int32 [n, 2] of

@@ -322,6 +322,72 @@ def test_one_loud_key_is_heard_just_inside_and_not_just_outside_a_chunk(dtype, H
             assert (share[H - 1] - vals[loud, G - 1]).abs().max() > 0.3       # and none of it when the chunk hides it
 
 
+# ---- the tensor-core kernel: clusters of every size, cut rows, single rows split over their keys ----
+
+def _step_context(segs, dev, graph=False):
+    from ninfer_amd_mi50_b200.parts.base import StepContext
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    rows, row_seg, row0 = [], [], [0]
+    for s, (p0, n) in enumerate(segs):
+        rows += list(range(p0, p0 + n)); row_seg += [s] * n; row0.append(len(rows))
+    T = len(rows)
+    return StepContext(dtype=torch.bfloat16, device=dev, T=T, S=len(segs), token_ids=mk([0] * T), positions=mk(rows),
+                       row_seg=mk(row_seg), seg_row0=mk(row0), seg_pos0=mk([p for p, _ in segs]),
+                       seg_slot=mk(list(range(len(segs)))), logit_rows=mk([T - 1]),
+                       seg_len_host=None if graph else [n for _, n in segs],
+                       seg_pos0_host=None if graph else [p for p, _ in segs],
+                       max_rows_per_seg=max(n for _, n in segs), max_context=max(p + n for p, n in segs)), rows, row_seg
+
+
+@pytest.mark.parametrize("H,G,D,Dv,chunk", [(4, 2, 64, 64, 48), (8, 8, 128, 128, 96), (8, 2, 128, 64, 0), (16, 4, 64, 128, 100),
+                                            (32, 32, 128, 128, 70), (12, 4, 64, 64, 64), (24, 8, 32, 48, 33), (3, 3, 16, 16, 7),
+                                            (5, 1, 48, 32, 200), (2, 1, 16, 80, 32), (1, 1, 128, 16, 0)])
+@pytest.mark.parametrize("segs,graph", [([(0, 75)], False), ([(37, 90), (199, 1), (0, 17), (130, 2)], False),
+                                         ([(199, 1), (64, 1), (63, 1), (0, 1), (31, 1), (32, 1)], False),
+                                         ([(199, 1), (96, 1), (95, 1), (0, 1)], True)])
+def test_tensor_core_attention_against_the_plain_rule_and_the_plain_kernel(H, G, D, Dv, chunk, segs, graph):
+    """The tensor-core kernel deals the heads out over a cluster of CTAs (1, 2, 4 or 8, by the sizes) that
+    read one another's scores; prompt portions that begin inside a chunk and end inside another, rows
+    at a chunk's first and last position, and steps of single rows, whose keys are cut into runs and
+    merged (also as a captured step sees them, without lengths on the host), are compared row by row
+    with the rule in float64 and with the plain kernel."""
+    from ninfer_amd_mi50_b200 import kernels
+    from ninfer_amd_mi50_b200.kernels import ops
+    dev = torch.device("cuda")
+    assert kernels.lib.load().nf_talking_attention_mma_heads_per_cta(H, G, D, Dv) > 0
+    gen = torch.Generator().manual_seed(H * 131 + D)
+    page, S = 16, len(segs)
+    n = max(p + k for p, k in segs)
+    per = (n + page - 1) // page
+    keys = (torch.randn((S, n, G, D), generator=gen) * 0.6).to(torch.bfloat16)
+    vals = torch.randn((S, n, G, Dv), generator=gen).to(torch.bfloat16)
+    order = (torch.randperm(S * per, generator=gen) + 1).reshape(S, per)
+    pages = torch.zeros((S * per + 1, page, G * (D + Dv)), dtype=torch.bfloat16)
+    for s in range(S):
+        for j in range(n):
+            pages[order[s, j // page], j % page] = torch.cat([keys[s, j].reshape(-1), vals[s, j].reshape(-1)])
+    talk = (torch.eye(H) * 0.8 + torch.randn((H, H), generator=gen) * 0.2).float()
+    sink = torch.linspace(1.5, -2.0, H).float()
+    ctx, rows, row_seg = _step_context(segs, dev, graph)
+    q = (torch.randn((len(rows), H, D), generator=gen) * 0.8).to(torch.bfloat16)
+    args = (q.reshape(len(rows), H * D).to(dev), H, G, D, Dv, pages.to(dev), order.to(torch.int32).to(dev), page, ctx,
+            chunk, D ** -0.5, talk.to(dev), sink.to(dev))
+    old = ops.TUNING["bf16_attention"]
+    try:
+        ops.TUNING["bf16_attention"] = "auto"
+        got = kernels.talking_attention(*args).double().cpu().reshape(len(rows), H, Dv)
+        ops.TUNING["bf16_attention"] = "generic"
+        slow = kernels.talking_attention(*args).double().cpu().reshape(len(rows), H, Dv)
+    finally:
+        ops.TUNING["bf16_attention"] = old
+    for r, (p, s) in enumerate(zip(rows, row_seg)):
+        want = plain_attention_row(q[r].double(), keys[s].double(), vals[s].double(), p, D ** -0.5, talk.double(),
+                                   sink.double(), chunk)
+        bound = 1.2e-2 * max(1.0, want.abs().max().item())            # the output is rounded to bfloat16
+        assert (got[r] - want).abs().max() <= bound, (r, p, s)
+        assert (got[r] - slow[r]).abs().max() <= bound, (r, p, s)
+
+
 # ---- pages, slots, long decoding ----------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
