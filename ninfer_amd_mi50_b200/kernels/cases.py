@@ -229,7 +229,26 @@ def case_window_attention(tokens: int, device, single: bool = False, context: in
                                                                         D ** -0.5, slopes, gate, 0))]
 
 
+def case_talking_attention(tokens: int, device, single: bool = False, context: int = 0, chunk: int = 1536):
+    """Softmax attention whose heads' scores are mixed before the softmax, over chunks of `chunk` positions and
+    with a sink (HQ query and key heads of 128): a prompt of `tokens` rows, or `tokens` decoded rows at `context`."""
+    from . import talking_attention
+    D = 128
+    ctx = _one_request(tokens, device, single, context)
+    held = (context + 1) if single else tokens
+    per = (held + PAGE - 1) // PAGE
+    pages = (torch.randn(ctx.S * per + 1, PAGE, HQ * 2 * D, device=device) * 0.5).bfloat16()
+    bt = torch.arange(ctx.S * per, dtype=torch.int32, device=device).view(ctx.S, per)
+    q = (torch.randn(tokens, HQ * D, device=device) * 0.5).bfloat16()
+    talk = torch.eye(HQ, device=device) * 0.8 + torch.randn(HQ, HQ, device=device) * 0.1
+    sink = torch.zeros(HQ, device=device)
+    return [("talking_attention", lambda: talking_attention(q, HQ, HQ, D, D, pages, bt, PAGE, ctx, chunk, D ** -0.5,
+                                                            talk, sink))]
+
+
 CASES = {
+    "talking_attention_prefill": lambda dev: case_talking_attention(2048, dev),
+    "talking_attention_decode8": lambda dev: case_talking_attention(8, dev, True, 2047),
     "linear_attention_prefill": lambda dev: case_linear_attention(2048, dev),
     "linear_attention_decode8": lambda dev: case_linear_attention(8, dev, True),
     "retention_prefill": lambda dev: case_linear_attention(2048, dev, dim=64, rotary=True),
