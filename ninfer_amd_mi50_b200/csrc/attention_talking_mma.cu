@@ -23,8 +23,9 @@
 //
 // A step of single rows may cut a row's keys into `nsplit` runs of blocks counted from the row's own
 // first block (its chunk's start), one cluster each; partial (m, l, O) go to a workspace and a second
-// kernel merges them in ascending order and adds the sink.  So a row's sums depend on its own
-// position and on nsplit only.
+// kernel merges them in ascending order and adds the sink.  A step with few tiles may cut the keys
+// into runs counted from position 0 in the same way, so that a long tile's blocks spread over SMs.
+// Either way a row's sums depend on its own position and on the runs' length only.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -181,10 +182,22 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     j_hi = max(j_hi, row_pos[r]);
   }
   const int b_first = j_lo / kTmKeys;
-  const bool partial = ws_o != nullptr;                // runs of blocks whose sums a second kernel merges
-  const int b_begin = partial ? b_first + split * blocks_per_split : b_first;
-  const int b_end = partial ? min(j_hi / kTmKeys + 1, b_begin + blocks_per_split) : j_hi / kTmKeys + 1;
+  // runs of blocks whose sums a second kernel merges: counted from the row's first block for steps of single
+  // rows, from position 0 for tiles of several rows (so that a row's runs do not depend on its neighbours)
+  const bool partial = ws_o != nullptr;
+  const int b_begin = !partial ? b_first : tiles ? max(b_first, split * blocks_per_split) : b_first + split * blocks_per_split;
+  const int b_end = !partial ? j_hi / kTmKeys + 1
+                             : min(j_hi / kTmKeys + 1, (tiles ? split * blocks_per_split : b_begin) + blocks_per_split);
   const int* bt = block_table + (size_t)seg * bt_width;
+
+  if (partial && b_begin >= b_end) {                    // none of the tile's keys in this run (the whole cluster leaves)
+    for (int i = tid; i < nrows * HC; i += kTmThreads) {
+      const size_t slot = ((size_t)(row0 + i / HC) * H + h0 + i % HC) * nsplit + split;
+      ws_ml[slot * 2] = -INFINITY;
+      ws_ml[slot * 2 + 1] = 0.f;
+    }
+    return;
+  }
 
   // eight threads a key row: the row's page is looked up once, then 16-byte copies at a stride of eight
   const int n16_k = nkv * D / 8, n16_v = nkv * Dv / 8;
@@ -529,7 +542,7 @@ extern "C" int nf_talking_attention_mma(const void* q, const void* pages, const 
   NF_REQUIRE(hc > 0, "talking attention (tensor cores): sizes H=%d G=%d D=%d Dv=%d do not fit", H, G, D, Dv);
   NF_REQUIRE(chunk >= 0 && page_size > 0 && nsplit >= 1 && blocks_per_split >= 1, "talking attention: bad chunk, page size or split");
   NF_REQUIRE((ws_o == nullptr) == (ws_ml == nullptr), "talking attention: one workspace without the other");
-  NF_REQUIRE(ws_o ? tiles == nullptr : nsplit == 1, "talking attention: only steps of single rows are split");
+  NF_REQUIRE(ws_o || nsplit == 1, "talking attention: runs of keys need the workspace");
   const int C = H / hc;
   const size_t smem = tm_layout(H, G, D, Dv, hc).total;
   const dim3 grid(n_tiles * C, nsplit);

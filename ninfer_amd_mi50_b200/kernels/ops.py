@@ -1475,7 +1475,11 @@ def head_norm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], q_no
 TALKING_TILE_ROWS = 32      # rows a tile of the tensor-core kernel
 TALKING_KEY_BLOCK = 32      # keys a block of that kernel
 TALKING_SPLIT_CTAS = 296    # steps of single rows: their keys are cut into runs until about this many CTAs run
-TALKING_SPLIT_BLOCKS = 16   # ... without chunks, into runs of this many blocks
+TALKING_SPLIT_BLOCKS = 16   # ... without chunks, into runs of this many blocks; so are the keys of steps with few tiles
+TALKING_MAX_RUNS = 16       # ... unless that made more runs than this
+# ... and only while the tiles' CTAs are fewer than this (a prompt of 2,048 tokens at head size 128: 265 -> 205 us
+# a layer with 128 CTAs, but 321 -> 390 us with 256, where the merge's traffic outweighs the better balance)
+TALKING_FEW_CTAS = 148
 
 
 def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: torch.Tensor,
@@ -1517,6 +1521,15 @@ def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: t
             ws_ml = torch.empty((T * H, nsplit, 2), dtype=torch.float32, device=q.device)
         else:
             tiles, n_tiles = ctx.chunked_query_tiles(TALKING_TILE_ROWS, chunk)
+            # few tiles (fewer CTAs than SMs) with many key blocks each: the keys are cut
+            # into runs of TALKING_SPLIT_BLOCKS blocks counted from position 0, so that the longest tile
+            # does not set the time; the runs are merged as those of single rows are
+            n_blocks = (int(ctx.max_context) + TALKING_KEY_BLOCK - 1) // TALKING_KEY_BLOCK
+            runs = (n_blocks + TALKING_SPLIT_BLOCKS - 1) // TALKING_SPLIT_BLOCKS
+            if n_tiles * (H // per_cta) < TALKING_FEW_CTAS and 2 <= runs <= TALKING_MAX_RUNS:
+                nsplit, per_split = runs, TALKING_SPLIT_BLOCKS
+                ws_o = torch.empty((T * H, nsplit, Dv), dtype=torch.float32, device=q.device)
+                ws_ml = torch.empty((T * H, nsplit, 2), dtype=torch.float32, device=q.device)
         _lib.call("nf_talking_attention_mma", _p(q), _p(pages), _p(block_table), c_int(block_table.shape[1]),
                   _p(ctx.positions), _p(ctx.seg_row0), _p(tiles), c_int(n_tiles), _p(talk), _p(sink), _p(out),
                   _p(ws_o), _p(ws_ml), c_int(T), c_int(H), c_int(G), c_int(D), c_int(Dv), c_int(page_size),

@@ -344,13 +344,15 @@ def _step_context(segs, dev, graph=False):
                                             (5, 1, 48, 32, 200), (2, 1, 16, 80, 32), (1, 1, 128, 16, 0)])
 @pytest.mark.parametrize("segs,graph", [([(0, 75)], False), ([(37, 90), (199, 1), (0, 17), (130, 2)], False),
                                          ([(199, 1), (64, 1), (63, 1), (0, 1), (31, 1), (32, 1)], False),
-                                         ([(199, 1), (96, 1), (95, 1), (0, 1)], True)])
+                                         ([(199, 1), (96, 1), (95, 1), (0, 1)], True),
+                                         ([(480, 100), (1030, 3)], False)])
 def test_tensor_core_attention_against_the_plain_rule_and_the_plain_kernel(H, G, D, Dv, chunk, segs, graph):
     """The tensor-core kernel deals the heads out over a cluster of CTAs (1, 2, 4 or 8, by the sizes) that
     read one another's scores; prompt portions that begin inside a chunk and end inside another, rows
     at a chunk's first and last position, and steps of single rows, whose keys are cut into runs and
-    merged (also as a captured step sees them, without lengths on the host), are compared row by row
-    with the rule in float64 and with the plain kernel."""
+    merged (also as a captured step sees them, without lengths on the host), and a step of few tiles far
+    into a request, whose keys are cut into runs counted from position 0, are compared row by row with the
+    rule in float64 and with the plain kernel."""
     from ninfer_amd_mi50_b200 import kernels
     from ninfer_amd_mi50_b200.kernels import ops
     dev = torch.device("cuda")
