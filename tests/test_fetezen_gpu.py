@@ -268,7 +268,7 @@ def plain_attention_row(q, keys, vals, pos, scale, talk, sink, chunk):
     return torch.einsum("hj,jhd->hd", p, v)
 
 
-@pytest.mark.parametrize("dtype,H,G,D,Dv", [(torch.float32, 4, 2, 16, 24), (torch.bfloat16, 4, 2, 16, 24), (torch.bfloat16, 4, 2, 64, 64),
+@pytest.mark.parametrize("dtype,H,G,D,Dv", [(torch.float32, 4, 2, 16, 24), (torch.bfloat16, 4, 2, 16, 24), (torch.bfloat16, 4, 1, 64, 48),
                                             (torch.bfloat16, 8, 1, 32, 16), (torch.float32, 3, 3, 12, 20), (torch.bfloat16, 16, 4, 128, 128)])
 @pytest.mark.parametrize("chunk", [37, 16, 64, 0, 150, 1])
 def test_one_loud_key_is_heard_just_inside_and_not_just_outside_a_chunk(dtype, H, G, D, Dv, chunk):
@@ -339,7 +339,7 @@ def _step_context(segs, dev, graph=False):
                        max_rows_per_seg=max(n for _, n in segs), max_context=max(p + n for p, n in segs)), rows, row_seg
 
 
-@pytest.mark.parametrize("H,G,D,Dv,chunk", [(4, 2, 64, 64, 48), (8, 8, 128, 128, 96), (8, 2, 128, 64, 0), (16, 4, 64, 128, 100),
+@pytest.mark.parametrize("H,G,D,Dv,chunk", [(4, 4, 64, 48, 48), (8, 8, 128, 128, 96), (8, 2, 128, 64, 0), (16, 4, 64, 128, 100),
                                             (32, 32, 128, 128, 70), (12, 4, 64, 64, 64), (24, 8, 32, 48, 33), (3, 3, 16, 16, 7),
                                             (5, 1, 48, 32, 200), (2, 1, 16, 80, 32), (1, 1, 128, 16, 0)])
 @pytest.mark.parametrize("segs,graph", [([(0, 75)], False), ([(37, 90), (199, 1), (0, 17), (130, 2)], False),
