@@ -216,7 +216,7 @@ __device__ __forceinline__ void load8(const float* p, float* out) {
 // The gated activation of a feed-forward's first product, from the gate's and the up projection's
 // float32 sums.  kind 1: silu(g) * u.  kind 2 (capped): g' = min(g, limit), u' = clamp(u, -limit,
 // limit); g' * sigmoid(alpha * g') * (u' + 1).
-enum GatedAct : int { kActNone = 0, kActSilu = 1, kActCapped = 2 };
+enum GatedAct : int { kActNone = 0, kActSilu = 1, kActCapped = 2, kActGeluErf = 3 };   // 3: no gate, the exact GELU of the sums
 struct GatedActParams {
   int kind;       // GatedAct
   float limit, alpha;
@@ -229,6 +229,7 @@ __device__ __forceinline__ float gated_act(float g, float u, int kind, float lim
   }
   return g / (1.f + expf(-g)) * u;
 }
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }
 __device__ __forceinline__ float gated_act(float g, float u, const GatedActParams& a) {
   return gated_act(g, u, a.kind, a.limit, a.alpha);
 }

@@ -296,6 +296,9 @@ grouped_gemm_tc_kernel(const __nv_bfloat16* __restrict__ Wp, const __grid_consta
                       v0 = __fdividef(v0, 1.f + __expf(-v0)) * __uint_as_float(u[c]);
                       v1 = __fdividef(v1, 1.f + __expf(-v1)) * __uint_as_float(u[c + 1]);
                     }
+                  } else if (act.kind == kActGeluErf) {
+                    v0 = gelu_erf(v0);
+                    v1 = gelu_erf(v1);
                   }
                   const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
                   pk[8 * j + c / 2] = *reinterpret_cast<const unsigned*>(&h);
@@ -388,9 +391,9 @@ extern "C" int nf_grouped_gemm_tc(const void* X, long long total_rows, const voi
   CUtensorMap mx, mx_half;
   if (int rc = make_map(&mx, X, total_rows, K, kXBox)) return rc;
   if (int rc = make_map(&mx_half, X, total_rows, K, kXBox / 2)) return rc;
-  NF_REQUIRE(swiglu >= 0 && swiglu <= 2, "grouped_gemm_tc: epilogue %d (0 none, 1 silu-gated, 2 capped)", swiglu);
+  NF_REQUIRE(swiglu >= 0 && swiglu <= 3, "grouped_gemm_tc: epilogue %d (0 none, 1 silu-gated, 2 capped, 3 ungated GELU)", swiglu);
   const GatedActParams act{swiglu, act_limit, act_alpha};
-  if (swiglu) return launch_tc<true, false>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, act, stream);
+  if (swiglu == kActSilu || swiglu == kActCapped) return launch_tc<true, false>(Wp, mx, mx_half, offsets, out, ldo, n_features, K, groups, act, stream);
   // two feature tiles an item once an expert's rows weigh about as much as a tile's weights
   // (decided by the counts the host knows: all rows, all groups)
   if (g_tc_pair && total_rows >= (long long)g_tc_pair_min_rows * groups)

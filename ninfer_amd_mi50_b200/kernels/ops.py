@@ -819,8 +819,10 @@ def moe_experts_sorted(xs: torch.Tensor, w13, w2, plan: MoePlan, act=None) -> to
     return moe_gemm2(moe_gemm1(xs, w13, plan, plan.top_k, sorted_rows=True, act=act), w2, plan, plan_is_older=True)
 
 
-def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False) -> torch.Tensor:
+def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False, gelu: bool = False) -> torch.Tensor:
     """Sorted pair p of expert e -> act[p] Wdown_e^T  [T*k, H].  `w2` is [E, H, I] or packed.
+    `gelu`: the exact GELU of the result (in the tensor-core kernel's epilogue, on the float32 sums;
+    a pass of its own after the other kernels).
 
     `plan_is_older`: the plan was complete before the kernel that produced `act` was launched
     (the usual order: router, first product, this).  The streaming kernel then starts fetching
@@ -844,15 +846,17 @@ def moe_gemm2(act: torch.Tensor, w2, plan: MoePlan, plan_is_older: bool = False)
                     None, 1, False, packed=True, group_map=plan.active, early_index=plan_is_older)
         else:
             _lib.call("nf_grouped_gemm_tc", _p(act), c_longlong(n), _p(w2.data), c_int(E), c_int(H),
-                      c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(0), c_float(0.0), c_float(0.0), _stream())
-        return y
+                      c_int(inner), _p(plan.offsets), _p(y), c_int(H), c_int(3 if gelu else 0), c_float(0.0),
+                      c_float(0.0), _stream())
+            return y
+        return gelu_erf_(y) if gelu else y
     path = "simt" if act.dtype == torch.float32 else _bf16_path(plan.num_tokens, inner, "bf16_moe")
     if path == "skinny":
         _skinny(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False,
                 group_map=plan.active, early_index=plan_is_older)
     else:
         _gemm_simt(act, inner, w2, H * inner, y, n, H, inner, E, plan.num_tokens, plan.offsets, None, 1, False)
-    return y
+    return gelu_erf_(y) if gelu else y
 
 
 _STREAM_WORK = {}
@@ -1582,17 +1586,17 @@ def table_route(table: torch.Tensor, ids: torch.Tensor, E: int) -> torch.Tensor:
     return idx
 
 
-def moe_rows_gemm(x: torch.Tensor, w, plan: "MoePlan", k: int, from_tokens: bool) -> torch.Tensor:
+def moe_rows_gemm(x: torch.Tensor, w, plan: "MoePlan", k: int, from_tokens: bool, gelu: bool = False) -> torch.Tensor:
     """One ungated product of the routed experts: sorted pair p of expert e -> x_p W_e^T.  With
     `from_tokens`, x is [T, K] and pair p reads token order[p] // k; otherwise x is [T*k, K] in
-    sorted order.  `w` is [E, N, K] or its packed form."""
+    sorted order.  `w` is [E, N, K] or its packed form.  `gelu`: the exact GELU of the result."""
     if not from_tokens:
-        return moe_gemm2(x, w, plan, plan_is_older=True)
+        return moe_gemm2(x, w, plan, plan_is_older=True, gelu=gelu)
     _chk(x, "x")
     T, K = x.shape
     packed = isinstance(w, PackedWeights)
     if packed and T > TUNING["skinny_moe_max_tokens"]:
-        return moe_gemm2(moe_gather(x, plan, k), w, plan, plan_is_older=True)
+        return moe_gemm2(moe_gather(x, plan, k), w, plan, plan_is_older=True, gelu=gelu)
     if packed:
         E, N = w.groups, w.n_features
     else:
@@ -1604,13 +1608,13 @@ def moe_rows_gemm(x: torch.Tensor, w, plan: "MoePlan", k: int, from_tokens: bool
     if packed:
         _skinny(x, K, w.data, w.group_stride, out, T * k, N, K, E, T, plan.offsets, plan.order, k, False,
                 packed=True, group_map=plan.active)
-        return out
+        return gelu_erf_(out) if gelu else out
     path = "simt" if x.dtype == torch.float32 else _bf16_path(T, K, "bf16_moe")
     if path == "skinny":
         _skinny(x, K, w, N * K, out, T * k, N, K, E, T, plan.offsets, plan.order, k, False, group_map=plan.active)
     else:
         _gemm_simt(x, K, w, N * K, out, T * k, N, K, E, T, plan.offsets, plan.order, k, False)
-    return out
+    return gelu_erf_(out) if gelu else out
 
 
 SAMPLE_MAX_TOP_K = 1024

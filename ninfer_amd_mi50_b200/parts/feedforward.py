@@ -457,7 +457,7 @@ class TableRoutedGelu(FeedForward):
         E, k = self.num_experts, self.top_k
         idx = kernels.table_route(self.table, ctx.token_ids, E)
         plan = kernels.moe_plan(idx, E)
-        a = kernels.gelu_erf_(kernels.moe_rows_gemm(x, self.w_up, plan, k, from_tokens=True))
+        a = kernels.moe_rows_gemm(x, self.w_up, plan, k, from_tokens=True, gelu=True)
         y = kernels.moe_rows_gemm(a, self.w_down, plan, k, from_tokens=False)
         shared = gate = None
         if self.has_shared:
