@@ -4,7 +4,8 @@ than a page and no multiple of one, a layer that sees every earlier position, on
 many as query heads, rotated dimensions fewer than the head and none at all, one residual stream,
 several, and none declared, one norm group and several, every expert chosen and one of many, with
 and without a shared expert, layers that read another layer's keys and values (with a chunk of
-their own), a layer without a feed-forward, with and without the cap on the logits."""
+their own), a layer without a feed-forward, with and without the cap on the logits; and one with
+heads of 128 and with 16 heads, which the tensor-core attention kernel serves with clusters."""
 
 import torch
 
@@ -74,7 +75,19 @@ AWKWARD = {
     ],
 }
 
-CONFIGS = {"sharing": (SHARING, 51), "plain": (PLAIN, 52), "awkward": (AWKWARD, 53)}
+# heads of 128 and many heads: the tensor-core attention kernel deals them out over clusters of two CTAs; a reader
+# of layer 0 with a longer chunk; key heads shared by two and by eight query heads; a layer that sees everything
+WIDE = {
+    "architecture": "Fetezen", "vocab": 131, "width": 128, "streams": 2, "logit_softcap": 20.0,
+    "norm": {"eps": 1e-5, "groups": 2},
+    "layers": [
+        layer(attention(8, 4, 128, 64, 0.09, chunk=48, rot=(1000.0, 64)), moe(32, 6, 2, shared=24)),
+        layer(attention(8, 4, 128, 64, 0.08, chunk=100, rot=(1000.0, 64), kv_from=0), dense(64)),
+        layer(attention(16, 2, 32, 32, 0.2, rot=(300.0, 16)), None),
+    ],
+}
+
+CONFIGS = {"sharing": (SHARING, 51), "plain": (PLAIN, 52), "awkward": (AWKWARD, 53), "wide": (WIDE, 54)}
 
 # factors that take the random weights (standard deviation 0.02) out of their nearly linear range
 LIVELY = {".mix.q": 6.0, ".mix.k": 6.0, ".mix.v": 4.0, ".q.b": 20.0, ".k.b": 20.0, ".v.b": 10.0, ".o.b": 10.0,
