@@ -1,7 +1,7 @@
 // The attention of attention_talking.cu (heads' scores mixed before the softmax, chunks, a sink) on
 // tensor cores, in bfloat16, for prompt portions and decoded tokens alike.
 //
-// The mixing ties all heads of a (row, key) pair together, so a tile is 32 consecutive rows of one
+// The mixing ties all heads of a (row, key) pair together, so a tile is 32 (or 16) consecutive rows of one
 // request with ALL heads, and the heads are dealt out over the CTAs of a thread-block cluster: CTA r
 // of C owns heads [r * HC, (r + 1) * HC), as score heads and as output heads.  Keys come in blocks
 // of 32 aligned to absolute positions, in ascending order.  For every block a CTA
@@ -36,7 +36,6 @@ namespace nf {
 
 namespace {
 
-constexpr int kTmRows = 32;        // rows a tile (two MMA tiles of 16)
 constexpr int kTmKeys = 32;        // keys a block
 constexpr int kTmThreads = 256;
 constexpr int kTmPad = 8;          // bfloat16 elements of padding a shared-memory row
@@ -79,6 +78,31 @@ __device__ __forceinline__ void tm_talk_row(const float* p, float* w) {
     for (int i = 0; i < HC; ++i) w[i] = p[i];
   }
 }
+__device__ __forceinline__ float2 tm_ld_cluster2(unsigned addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
+}
+template <int KPT>
+__device__ __forceinline__ void tm_ld_remote(unsigned addr, float* v) {
+  if constexpr (KPT == 4) {
+    const float4 t = tm_ld_cluster4(addr);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    const float2 t = tm_ld_cluster2(addr);
+    v[0] = t.x; v[1] = t.y;
+  }
+}
+template <int KPT>
+__device__ __forceinline__ void tm_ld_local(const float* p, float* v) {
+  if constexpr (KPT == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    const float2 t = *reinterpret_cast<const float2*>(p);
+    v[0] = t.x; v[1] = t.y;
+  }
+}
 __device__ __forceinline__ void tm_cp16(unsigned dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -89,7 +113,7 @@ struct TmLayout {
   size_t q, k, v, s, p, talk, alpha, l, pos, lo, total;
 };
 
-__host__ __device__ inline TmLayout tm_layout(int H, int G, int D, int Dv, int HC) {
+__host__ __device__ inline TmLayout tm_layout(int H, int G, int D, int Dv, int HC, int rows) {
   TmLayout L;
   const int rep = H / G;
   L.nkv = (HC + rep - 1) / rep + ((HC % rep != 0 && rep % HC != 0) ? 1 : 0);
@@ -98,16 +122,16 @@ __host__ __device__ inline TmLayout tm_layout(int H, int G, int D, int Dv, int H
   L.KS = L.nkv * D + kTmPad;
   L.VS = L.nkv * Dv + kTmPad;
   size_t o = 0;
-  L.q = o; o += (size_t)kTmRows * L.QS * 2;
+  L.q = o; o += (size_t)rows * L.QS * 2;
   L.k = o; o += (size_t)kTmKeys * L.KS * 2;
   L.v = o; o += (size_t)kTmKeys * L.VS * 2;
-  L.s = o; o += (size_t)2 * HC * kTmRows * kTmSP * 4;
-  L.p = o; o += (size_t)2 * HC * kTmRows * kTmPP * 2;
+  L.s = o; o += (size_t)2 * HC * rows * kTmSP * 4;
+  L.p = o; o += (size_t)2 * HC * rows * kTmPP * 2;
   L.talk = o; o += (size_t)H * HC * 4;
-  L.alpha = o; o += (size_t)HC * kTmRows * 4;
-  L.l = o; o += (size_t)HC * kTmRows * 4;
-  L.pos = o; o += kTmRows * 4;
-  L.lo = o; o += kTmRows * 4;
+  L.alpha = o; o += (size_t)HC * rows * 4;
+  L.l = o; o += (size_t)HC * rows * 4;
+  L.pos = o; o += rows * 4;
+  L.lo = o; o += rows * 4;
   L.total = (o + 15) & ~(size_t)15;
   return L;
 }
@@ -117,7 +141,7 @@ __host__ __device__ inline TmLayout tm_layout(int H, int G, int D, int Dv, int H
 // tiles: int32 [n_tiles, 2] of (segment, first row); null when every segment brings one row (tile i is
 // segment i).  ws_o float32 [T * H, nsplit, Dv], ws_ml float32 [T * H, nsplit, 2], or both null: with them
 // the CTAs of run `blockIdx.y` write partial sums there, which the merge kernel adds up with the sink.
-template <int HC, int NU>      // heads a CTA; (head, 16 columns) units of the second product a warp
+template <int HC, int NU, int ROWS>      // heads a CTA; (head, 16 columns) units of the second product a warp; rows a tile (32 or 16)
 __global__ void __launch_bounds__(kTmThreads, 1)
 talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                              const int* __restrict__ block_table, int bt_width, const int* __restrict__ positions,
@@ -126,7 +150,9 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
                              __nv_bfloat16* __restrict__ out, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                              int H, int G, int D, int Dv, int page_size, int num_pages, int chunk, float scale,
                              int nsplit, int blocks_per_split) {
-  constexpr int MT = kTmRows / 16;
+  constexpr int MT = ROWS / 16;
+  constexpr int KPT = kTmKeys * ROWS / kTmThreads;     // keys a mixing thread: 4 or 2
+  constexpr int LPR = kTmKeys / KPT;                   // mixing threads a row
   constexpr int NW = kTmThreads / 32;
   extern __shared__ __align__(16) unsigned char tm_raw[];
   cg::cluster_group cluster = cg::this_cluster();
@@ -134,7 +160,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   const int rank = (int)cluster.block_rank();
   const int tile = blockIdx.x / C, split = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const TmLayout L = tm_layout(H, G, D, Dv, HC);
+  const TmLayout L = tm_layout(H, G, D, Dv, HC, ROWS);
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(tm_raw + L.q);
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(tm_raw + L.k);
   __nv_bfloat16* Vs = reinterpret_cast<__nv_bfloat16*>(tm_raw + L.v);
@@ -159,8 +185,8 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   chain_wait(q, pages);
   const int seg = tiles ? tiles[2 * tile] : tile;
   const int row0 = tiles ? tiles[2 * tile + 1] : seg_row0[tile];
-  const int nrows = min(kTmRows, seg_row0[seg + 1] - row0);
-  if (tid < kTmRows) {
+  const int nrows = min(ROWS, seg_row0[seg + 1] - row0);
+  if (tid < ROWS) {
     const int p = tid < nrows ? positions[row0 + tid] : -1;
     row_pos[tid] = p;
     row_lo[tid] = p < 0 ? INT_MAX : (chunk > 0 ? (p / chunk) * chunk : 0);
@@ -168,7 +194,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   // the tile's queries of this CTA's heads, 16 bytes a copy
   {
     const int chunks = HC * D / 8;
-    for (int i = tid; i < kTmRows * chunks; i += kTmThreads) {
+    for (int i = tid; i < ROWS * chunks; i += kTmThreads) {
       const int r = i / chunks, c = (i - r * chunks) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (r < nrows) v = *reinterpret_cast<const uint4*>(q + (size_t)(row0 + r) * H * D + (size_t)h0 * D + c);
@@ -177,7 +203,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   }
   __syncthreads();
   int j_lo = INT_MAX, j_hi = -1;
-  for (int r = 0; r < kTmRows; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     j_lo = min(j_lo, row_lo[r]);
     j_hi = max(j_hi, row_pos[r]);
   }
@@ -220,9 +246,9 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  // the mixing thread's place: row mi, keys 4 kq .. 4 kq + 3 of the block, all of this CTA's heads (so every
-  // raw score is read once a CTA, and a warp's reads of a row are 128 consecutive bytes)
-  const int mi = tid >> 3, kq = tid & 7;
+  // the mixing thread's place: row mi, keys KPT kq .. of the block (four with 32 rows a tile, two with 16), all
+  // of this CTA's heads (so every raw score is read once a CTA, and a row's reads are 128 consecutive bytes)
+  const int mi = tid / LPR, kq = tid % LPR;
   const int my_pos = row_pos[mi], my_lo = row_lo[mi];
   const bool with_sink = sink != nullptr && !partial;
   float m_run[HC], l_run[HC];
@@ -284,7 +310,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
       }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        float* dst = Ss + ((size_t)(buf * HC + g) * kTmRows + mt * 16 + (lane >> 2)) * kTmSP + kh * 16 + (lane & 3) * 2;
+        float* dst = Ss + ((size_t)(buf * HC + g) * ROWS + mt * 16 + (lane >> 2)) * kTmSP + kh * 16 + (lane & 3) * 2;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
           *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(s[mt][nt][0] * scale, s[mt][nt][1] * scale);
@@ -296,98 +322,94 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
     fetch(blk + 1, false);                              // the keys' buffer is free
     // ---- 2. and 3. mixing, mask, maxima, sums, weights ----
     {
-      float acc[HC][4];
+      float acc[HC][KPT];
 #pragma unroll
-      for (int h = 0; h < HC; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
-      const unsigned s_ofs = (unsigned)((((size_t)buf * HC * kTmRows + mi) * kTmSP + kq * 4) * sizeof(float));
+      for (int h = 0; h < HC; ++h)
+#pragma unroll
+        for (int k = 0; k < KPT; ++k) acc[h][k] = 0.f;
+      const unsigned s_ofs = (unsigned)((((size_t)buf * HC * ROWS + mi) * kTmSP + kq * KPT) * sizeof(float));
       // own scores first, then the other CTAs' in a round that starts behind this CTA's rank, so that no
       // CTA's shared memory is asked by all the others at once; the reads of the next CTA's scores are
       // in flight while this one's are mixed
-      float4 sv[HC];
+      float sv[HC][KPT];
       if (C > 1) {
         const unsigned src = tm_mapa(tm_smem(Ss), (unsigned)(rank + 1 < C ? rank + 1 : 0)) + s_ofs;
 #pragma unroll
-        for (int gl = 0; gl < HC; ++gl) sv[gl] = tm_ld_cluster4(src + (unsigned)(gl * kTmRows * kTmSP * sizeof(float)));
+        for (int gl = 0; gl < HC; ++gl) tm_ld_remote<KPT>(src + (unsigned)(gl * ROWS * kTmSP * sizeof(float)), sv[gl]);
       }
       {
         const float* src = Ss + s_ofs / sizeof(float);
         const float* tk = talk_s + (size_t)rank * HC * HC;
 #pragma unroll
         for (int gl = 0; gl < HC; ++gl) {
-          const float4 lv = *reinterpret_cast<const float4*>(src + (size_t)gl * kTmRows * kTmSP);
-          float w[HC];
+          float lv[KPT], w[HC];
+          tm_ld_local<KPT>(src + (size_t)gl * ROWS * kTmSP, lv);
           tm_talk_row<HC>(tk + gl * HC, w);
 #pragma unroll
-          for (int h = 0; h < HC; ++h) {
-            acc[h][0] = fmaf(w[h], lv.x, acc[h][0]);
-            acc[h][1] = fmaf(w[h], lv.y, acc[h][1]);
-            acc[h][2] = fmaf(w[h], lv.z, acc[h][2]);
-            acc[h][3] = fmaf(w[h], lv.w, acc[h][3]);
-          }
+          for (int h = 0; h < HC; ++h)
+#pragma unroll
+            for (int k = 0; k < KPT; ++k) acc[h][k] = fmaf(w[h], lv[k], acc[h][k]);
         }
       }
       for (int step = 1; step < C; ++step) {
         const int c = rank + step < C ? rank + step : rank + step - C;
         const float* tk = talk_s + (size_t)c * HC * HC;
-        float4 cur[HC];
+        float cur[HC][KPT];
 #pragma unroll
-        for (int gl = 0; gl < HC; ++gl) cur[gl] = sv[gl];
+        for (int gl = 0; gl < HC; ++gl)
+#pragma unroll
+          for (int k = 0; k < KPT; ++k) cur[gl][k] = sv[gl][k];
         if (step + 1 < C) {
           const int cn = c + 1 < C ? c + 1 : 0;
           const unsigned src = tm_mapa(tm_smem(Ss), (unsigned)cn) + s_ofs;
 #pragma unroll
-          for (int gl = 0; gl < HC; ++gl) sv[gl] = tm_ld_cluster4(src + (unsigned)(gl * kTmRows * kTmSP * sizeof(float)));
+          for (int gl = 0; gl < HC; ++gl) tm_ld_remote<KPT>(src + (unsigned)(gl * ROWS * kTmSP * sizeof(float)), sv[gl]);
         }
 #pragma unroll
         for (int gl = 0; gl < HC; ++gl) {
           float w[HC];
           tm_talk_row<HC>(tk + gl * HC, w);
 #pragma unroll
-          for (int h = 0; h < HC; ++h) {
-            acc[h][0] = fmaf(w[h], cur[gl].x, acc[h][0]);
-            acc[h][1] = fmaf(w[h], cur[gl].y, acc[h][1]);
-            acc[h][2] = fmaf(w[h], cur[gl].z, acc[h][2]);
-            acc[h][3] = fmaf(w[h], cur[gl].w, acc[h][3]);
-          }
+          for (int h = 0; h < HC; ++h)
+#pragma unroll
+            for (int k = 0; k < KPT; ++k) acc[h][k] = fmaf(w[h], cur[gl][k], acc[h][k]);
         }
       }
-      const int j = blk * kTmKeys + kq * 4;
-      bool seen[4];
+      const int j = blk * kTmKeys + kq * KPT;
+      bool seen[KPT];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) seen[k] = j + k >= my_lo && j + k <= my_pos;
+      for (int k = 0; k < KPT; ++k) seen[k] = j + k >= my_lo && j + k <= my_pos;
 #pragma unroll
       for (int h = 0; h < HC; ++h) {
         float mx = -INFINITY;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < KPT; ++k) {
           if (!seen[k]) acc[h][k] = -INFINITY;
           mx = fmaxf(mx, acc[h][k]);
         }
 #pragma unroll
-        for (int d = 1; d < 8; d <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+        for (int d = 1; d < LPR; d <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
         const float m_new = fmaxf(m_run[h], mx);
         const float alpha = (m_run[h] == -INFINITY) ? 0.f : __expf(m_run[h] - m_new);
         float sum = 0.f;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < KPT; ++k) {
           acc[h][k] = seen[k] ? __expf(acc[h][k] - m_new) : 0.f;
           sum += acc[h][k];
         }
 #pragma unroll
-        for (int d = 1; d < 8; d <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        for (int d = 1; d < LPR; d <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
         m_run[h] = m_new;
         l_run[h] = l_run[h] * alpha + sum;
-        const __nv_bfloat162 b01 = __floats2bfloat162_rn(acc[h][0], acc[h][1]);
-        const __nv_bfloat162 b23 = __floats2bfloat162_rn(acc[h][2], acc[h][3]);
-        const __nv_bfloat162 r01 = __floats2bfloat162_rn(acc[h][0] - __bfloat162float(b01.x), acc[h][1] - __bfloat162float(b01.y));
-        const __nv_bfloat162 r23 = __floats2bfloat162_rn(acc[h][2] - __bfloat162float(b23.x), acc[h][3] - __bfloat162float(b23.y));
-        uint2 hi, lo;
-        hi.x = *reinterpret_cast<const unsigned*>(&b01); hi.y = *reinterpret_cast<const unsigned*>(&b23);
-        lo.x = *reinterpret_cast<const unsigned*>(&r01); lo.y = *reinterpret_cast<const unsigned*>(&r23);
-        __nv_bfloat16* pd = Ps + ((size_t)h * kTmRows + mi) * kTmPP + kq * 4;
-        *reinterpret_cast<uint2*>(pd) = hi;
-        *reinterpret_cast<uint2*>(pd + (size_t)HC * kTmRows * kTmPP) = lo;
-        if (kq == 0) alpha_s[h * kTmRows + mi] = alpha;
+        __nv_bfloat16* pd = Ps + ((size_t)h * ROWS + mi) * kTmPP + kq * KPT;
+#pragma unroll
+        for (int k = 0; k < KPT; k += 2) {
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(acc[h][k], acc[h][k + 1]);
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[h][k] - __bfloat162float(hi.x), acc[h][k + 1] - __bfloat162float(hi.y));
+          *reinterpret_cast<__nv_bfloat162*>(pd + k) = hi;
+          *reinterpret_cast<__nv_bfloat162*>(pd + (size_t)HC * ROWS * kTmPP + k) = lo;
+        }
+        if (kq == 0) alpha_s[h * ROWS + mi] = alpha;
       }
     }
     asm volatile("cp.async.wait_group 1;" ::: "memory");
@@ -399,14 +421,14 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
         const int h = unit_h[k];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          const float a_lo = alpha_s[h * kTmRows + mt * 16 + (lane >> 2)], a_hi = alpha_s[h * kTmRows + mt * 16 + 8 + (lane >> 2)];
+          const float a_lo = alpha_s[h * ROWS + mt * 16 + (lane >> 2)], a_hi = alpha_s[h * ROWS + mt * 16 + 8 + (lane >> 2)];
 #pragma unroll
           for (int nt = 0; nt < 2; ++nt) {
             o[k][mt][nt][0] *= a_lo; o[k][mt][nt][1] *= a_lo;
             o[k][mt][nt][2] *= a_hi; o[k][mt][nt][3] *= a_hi;
           }
         }
-        const unsigned pa = tm_smem(Ps + (h * kTmRows + (lane & 15)) * kTmPP + (lane >> 4) * 8);
+        const unsigned pa = tm_smem(Ps + (h * ROWS + (lane & 15)) * kTmPP + (lane >> 4) * 8);
         const unsigned va = tm_smem(Vs + ((lane & 7) + ((lane >> 3) & 1) * 8) * VS + unit_v[k] + (lane >> 4) * 8);
 #pragma unroll
         for (int ks = 0; ks < kTmKeys / 16; ++ks) {
@@ -416,7 +438,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
           for (int mt = 0; mt < MT; ++mt) {
             unsigned a0, a1, a2, a3, l0, l1, l2, l3;
             tm_ldm4(pa + (mt * 16 * kTmPP + ks * 16) * 2, a0, a1, a2, a3);
-            tm_ldm4(pa + (HC * kTmRows * kTmPP + mt * 16 * kTmPP + ks * 16) * 2, l0, l1, l2, l3);
+            tm_ldm4(pa + (HC * ROWS * kTmPP + mt * 16 * kTmPP + ks * 16) * 2, l0, l1, l2, l3);
             tm_mma(o[k][mt][0], a0, a1, a2, a3, b0, b1);
             tm_mma(o[k][mt][1], a0, a1, a2, a3, b2, b3);
             tm_mma(o[k][mt][0], l0, l1, l2, l3, b0, b1);
@@ -433,7 +455,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
   if (kq == 0) {
 #pragma unroll
     for (int h = 0; h < HC; ++h) {
-      l_s[h * kTmRows + mi] = l_run[h];
+      l_s[h * ROWS + mi] = l_run[h];
       if (partial && mi < nrows) {
         const size_t slot = ((size_t)(row0 + mi) * H + h0 + h) * nsplit + split;
         ws_ml[slot * 2] = m_run[h];
@@ -459,7 +481,7 @@ talking_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfl
           for (int nt = 0; nt < 2; ++nt)
             *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[k][mt][nt][half * 2], o[k][mt][nt][half * 2 + 1]);
         } else {
-          const float l = l_s[h * kTmRows + r];
+          const float l = l_s[h * ROWS + r];
           const float inv = l > 0.f ? 1.f / l : 0.f;
           __nv_bfloat16* dst = out + (size_t)(row0 + r) * H * Dv + (size_t)(h0 + h) * Dv + col;
 #pragma unroll
@@ -500,20 +522,36 @@ __global__ void talking_attention_merge_kernel(const float* __restrict__ ws_o, c
 }
 
 static int g_tm_max_heads = 8;
+static int g_tm_rows = 0;      // 0: 32 rows a tile where they fit, else 16; 16 or 32: only that
 
-// Heads a CTA: the most that fit (fewer CTAs share a tile's keys then), 0 if no split of the heads does.
-static int tm_heads_per_cta(int H, int G, int D, int Dv) {
-  if (H <= 0 || G <= 0 || H % G != 0 || D < 16 || Dv < 16 || D % 16 != 0 || Dv % 16 != 0) return 0;
+// Heads a CTA and rows a tile.  The most heads that fit with the given rows (fewer CTAs a cluster: what crosses
+// between the SMs of a cluster falls with their number); hc = 0 if no split of the heads fits.
+struct TmShape {
+  int hc, rows;
+};
+static TmShape tm_shape_rows(int H, int G, int D, int Dv, int rows) {
+  if (g_tm_rows != 0 && rows != g_tm_rows) return {0, 0};
   for (int hc = 8; hc >= 1; --hc) {
-    if (H % hc != 0) continue;
+    if (H % hc != 0 || hc > g_tm_max_heads) continue;
     const int c = H / hc;
     if (c != 1 && c != 2 && c != 4 && c != 8) continue;
-    if (hc > g_tm_max_heads) continue;
-    if (hc * Dv > 512) continue;                        // 64 accumulators a thread
-    if (tm_layout(H, G, D, Dv, hc).total > 227 * 1024) continue;
-    return hc;
+    if (hc * Dv * rows > 512 * 32) continue;            // 64 accumulators a thread
+    if (tm_layout(H, G, D, Dv, hc, rows).total > 227 * 1024) continue;
+    return {hc, rows};
   }
-  return 0;
+  return {0, 0};
+}
+// Steps of single rows take tiles of 16 rows (a tile holds one row, and more heads a CTA fit).  Prompt portions
+// take tiles of 32 rows, unless that makes clusters of 8 CTAs where tiles of 16 rows make smaller ones (measured,
+// a prompt of 2,048 tokens at head size 128: 205 / 319 / 842 us a layer with 32 rows and 4 heads a CTA at 8 / 16 /
+// 32 heads, 241 / 360 / 735 us with 16 rows and 8 heads a CTA).
+static TmShape tm_shape(int H, int G, int D, int Dv, bool single) {
+  if (H <= 0 || G <= 0 || H % G != 0 || D < 16 || Dv < 16 || D % 16 != 0 || Dv % 16 != 0) return {0, 0};
+  const TmShape tall = tm_shape_rows(H, G, D, Dv, 32), flat = tm_shape_rows(H, G, D, Dv, 16);
+  if (tall.hc == 0) return flat;
+  if (flat.hc == 0) return tall;
+  if (single) return flat;
+  return (H / tall.hc == 8 && H / flat.hc < 8) ? flat : tall;
 }
 
 }  // namespace nf
@@ -522,8 +560,18 @@ using namespace nf;
 
 // The heads a CTA of the tensor-core kernel takes at these sizes (a tile's cluster is H / that many CTAs);
 // 0: the kernel does not take them, and the plain kernel serves.
-extern "C" int nf_talking_attention_mma_heads_per_cta(int H, int G, int D, int Dv) {
-  return tm_heads_per_cta(H, G, D, Dv);
+// `single`: for a step whose segments bring one row each.
+extern "C" int nf_talking_attention_mma_heads_per_cta(int H, int G, int D, int Dv, int single) {
+  return tm_shape(H, G, D, Dv, single != 0).hc;
+}
+// ... and the rows of its tiles (32 or 16).
+extern "C" int nf_talking_attention_mma_tile_rows(int H, int G, int D, int Dv, int single) {
+  return tm_shape(H, G, D, Dv, single != 0).rows;
+}
+// Tiles of 16 or of 32 rows only; 0: the larger that fits.
+extern "C" int nf_set_talking_attention_mma_tile_rows(int rows) {
+  g_tm_rows = rows == 16 || rows == 32 ? rows : 0;
+  return 0;
 }
 
 // At most this many heads a CTA (1 to 8): fewer heads make larger clusters of lighter CTAs.
@@ -538,29 +586,37 @@ extern "C" int nf_talking_attention_mma(const void* q, const void* pages, const 
                                         int T, int H, int G, int D, int Dv, int page_size, int num_pages, int chunk,
                                         float scale, int nsplit, int blocks_per_split, cudaStream_t stream) {
   if (T == 0 || n_tiles == 0) return 0;
-  const int hc = tm_heads_per_cta(H, G, D, Dv);
+  const TmShape shape = tm_shape(H, G, D, Dv, tiles == nullptr);
+  const int hc = shape.hc;
   NF_REQUIRE(hc > 0, "talking attention (tensor cores): sizes H=%d G=%d D=%d Dv=%d do not fit", H, G, D, Dv);
   NF_REQUIRE(chunk >= 0 && page_size > 0 && nsplit >= 1 && blocks_per_split >= 1, "talking attention: bad chunk, page size or split");
   NF_REQUIRE((ws_o == nullptr) == (ws_ml == nullptr), "talking attention: one workspace without the other");
   NF_REQUIRE(ws_o || nsplit == 1, "talking attention: runs of keys need the workspace");
   const int C = H / hc;
-  const size_t smem = tm_layout(H, G, D, Dv, hc).total;
+  const size_t smem = tm_layout(H, G, D, Dv, hc, shape.rows).total;
   const dim3 grid(n_tiles * C, nsplit);
   const int units = hc * (Dv / 16);
   const __nv_bfloat16* qq = (const __nv_bfloat16*)q;
   const __nv_bfloat16* pg = (const __nv_bfloat16*)pages;
-#define NF_TM(HC, NU)                                                                                                 \
+#define NF_TM(HC, NU, ROWS)                                                                                           \
   do {                                                                                                                \
-    cudaFuncSetAttribute(talking_attention_mma_kernel<HC, NU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    launch_chained_cluster(talking_attention_mma_kernel<HC, NU>, grid, dim3(kTmThreads), smem, stream, C, qq, pg,     \
-                           block_table, bt_width, positions, seg_row0, tiles, talk, sink, (__nv_bfloat16*)out, ws_o,  \
-                           ws_ml, H, G, D, Dv, page_size, num_pages, chunk, scale, nsplit, blocks_per_split);         \
+    cudaFuncSetAttribute(talking_attention_mma_kernel<HC, NU, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                         (int)smem);                                                                                  \
+    launch_chained_cluster(talking_attention_mma_kernel<HC, NU, ROWS>, grid, dim3(kTmThreads), smem, stream, C, qq,   \
+                           pg, block_table, bt_width, positions, seg_row0, tiles, talk, sink, (__nv_bfloat16*)out,    \
+                           ws_o, ws_ml, H, G, D, Dv, page_size, num_pages, chunk, scale, nsplit, blocks_per_split);   \
   } while (0)
-#define NF_TM_HC(HC)                   \
-  do {                                 \
-    if (units <= 8) NF_TM(HC, 1);      \
-    else if (units <= 16) NF_TM(HC, 2); \
-    else NF_TM(HC, 4);                 \
+#define NF_TM_HC(HC)                                   \
+  do {                                                 \
+    if (shape.rows == 32) {                            \
+      if (units <= 8) NF_TM(HC, 1, 32);                \
+      else if (units <= 16) NF_TM(HC, 2, 32);          \
+      else NF_TM(HC, 4, 32);                           \
+    } else {                                           \
+      if (units <= 16) NF_TM(HC, 2, 16);               \
+      else if (units <= 32) NF_TM(HC, 4, 16);          \
+      else NF_TM(HC, 8, 16);                           \
+    }                                                  \
   } while (0)
   switch (hc) {
     case 1: NF_TM_HC(1); break;

@@ -1476,7 +1476,6 @@ def head_norm_rope_append(proj: torch.Tensor, bias: Optional[torch.Tensor], q_no
     return q
 
 
-TALKING_TILE_ROWS = 32      # rows a tile of the tensor-core kernel
 TALKING_KEY_BLOCK = 32      # keys a block of that kernel
 TALKING_SPLIT_CTAS = 296    # steps of single rows: their keys are cut into runs until about this many CTAs run
 TALKING_SPLIT_BLOCKS = 16   # ... without chunks, into runs of this many blocks; so are the keys of steps with few tiles
@@ -1498,11 +1497,12 @@ def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: t
     if T == 0:
         return out
     per_cta = 0
+    single = getattr(ctx, "all_single", False) or getattr(ctx, "seg_len_host", None) is None
     if q.dtype == torch.bfloat16 and TUNING["bf16_attention"] != "generic":
-        per_cta = _lib.load().nf_talking_attention_mma_heads_per_cta(c_int(H), c_int(G), c_int(D), c_int(Dv))
+        per_cta = _lib.load().nf_talking_attention_mma_heads_per_cta(c_int(H), c_int(G), c_int(D), c_int(Dv),
+                                                                     c_int(1 if single else 0))
     if per_cta > 0:
-        # tensor cores: tiles of 32 rows with all heads, the heads dealt out over a cluster's CTAs
-        single = getattr(ctx, "all_single", False) or getattr(ctx, "seg_len_host", None) is None
+        # tensor cores: tiles of 32 or 16 rows with all heads, the heads dealt out over a cluster's CTAs
         nsplit, per_split, ws_o, ws_ml = 1, 1, None, None
         if single:
             # one row a segment: the kernel numbers the tiles itself, and a row's keys (from its chunk's
@@ -1524,7 +1524,8 @@ def talking_attention(q: torch.Tensor, H: int, G: int, D: int, Dv: int, pages: t
             ws_o = torch.empty((T * H, nsplit, Dv), dtype=torch.float32, device=q.device)
             ws_ml = torch.empty((T * H, nsplit, 2), dtype=torch.float32, device=q.device)
         else:
-            tiles, n_tiles = ctx.chunked_query_tiles(TALKING_TILE_ROWS, chunk)
+            tile_rows = _lib.load().nf_talking_attention_mma_tile_rows(c_int(H), c_int(G), c_int(D), c_int(Dv), c_int(0))
+            tiles, n_tiles = ctx.chunked_query_tiles(tile_rows, chunk)
             # few tiles (fewer CTAs than SMs) with many key blocks each: the keys are cut
             # into runs of TALKING_SPLIT_BLOCKS blocks counted from position 0, so that the longest tile
             # does not set the time; the runs are merged as those of single rows are

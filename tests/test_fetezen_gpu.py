@@ -356,7 +356,7 @@ def test_tensor_core_attention_against_the_plain_rule_and_the_plain_kernel(H, G,
     from ninfer_amd_mi50_b200 import kernels
     from ninfer_amd_mi50_b200.kernels import ops
     dev = torch.device("cuda")
-    assert kernels.lib.load().nf_talking_attention_mma_heads_per_cta(H, G, D, Dv) > 0
+    assert kernels.lib.load().nf_talking_attention_mma_heads_per_cta(H, G, D, Dv, 0) > 0
     gen = torch.Generator().manual_seed(H * 131 + D)
     page, S = 16, len(segs)
     n = max(p + k for p, k in segs)
