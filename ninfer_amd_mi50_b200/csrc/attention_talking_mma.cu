@@ -5,17 +5,17 @@
 // request with ALL heads, and the heads are dealt out over the CTAs of a thread-block cluster: CTA r
 // of C owns heads [r * HC, (r + 1) * HC), as score heads and as output heads.  Keys come in blocks
 // of 32 aligned to absolute positions, in ascending order.  For every block a CTA
-//   1. computes its own heads' raw scores S_g = Q_g K^T * scale [32 x 32] with mma.sync into its
-//      shared memory (float32): a warp takes (head, 16 keys), both halves of the rows,
+//   1. computes its own heads' raw scores S_g = Q_g K^T * scale [rows x 32] with mma.sync into its
+//      shared memory (float32): a warp takes (head, 16 keys), all the rows,
 //   2. meets the others at a cluster barrier and reads ALL heads' raw scores, its own and the other
 //      CTAs' through distributed shared memory, to mix them for its output heads:
-//      S'_h = sum_g talk[h, g] S_g, in float32 on the vector units; a thread owns one row, four
-//      consecutive keys and all of the CTA's heads, so every raw score is read once a CTA,
-//   3. masks (j <= i, same chunk), updates the row's maximum and sum (a shuffle among the eight
+//      S'_h = sum_g talk[h, g] S_g, in float32 on the vector units; a thread owns one row, four (or
+//      two) consecutive keys and all of the CTA's heads, so every raw score is read once a CTA,
+//   3. masks (j <= i, same chunk), updates the row's maximum and sum (a shuffle among the 8 or 16
 //      threads of a row), and writes the weights as two bfloat16 halves (the rounding and what it
 //      left: 16 bits of mantissa together),
 //   4. adds P_h V to its output heads' accumulators (registers) with mma.sync: a warp takes
-//      (head, 16 columns), both halves of the rows.
+//      (head, 16 columns), all the rows.
 // The raw scores are double buffered, so one cluster barrier a block is enough: a CTA that writes
 // block b + 2 has passed barrier b + 1, which every CTA reaches only after it has mixed block b.
 // Keys and values of the CTA's heads arrive by cp.async, the next block's keys while this block is
