@@ -215,8 +215,9 @@ __device__ __forceinline__ void load8(const float* p, float* out) {
 
 // The gated activation of a feed-forward's first product, from the gate's and the up projection's
 // float32 sums.  kind 1: silu(g) * u.  kind 2 (capped): g' = min(g, limit), u' = clamp(u, -limit,
-// limit); g' * sigmoid(alpha * g') * (u' + 1).
-enum GatedAct : int { kActNone = 0, kActSilu = 1, kActCapped = 2, kActGeluErf = 3 };   // 3: no gate, the exact GELU of the sums
+// limit); g' * sigmoid(alpha * g') * (u' + 1).  kind 4: gelu_tanh(g) * u with
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+enum GatedAct : int { kActNone = 0, kActSilu = 1, kActCapped = 2, kActGeluErf = 3, kActGeluTanh = 4 };   // 3: no gate, the exact GELU of the sums
 struct GatedActParams {
   int kind;       // GatedAct
   float limit, alpha;
@@ -227,6 +228,8 @@ __device__ __forceinline__ float gated_act(float g, float u, int kind, float lim
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.f + expf(-alpha * g)) * (u + 1.f);
   }
+  if (kind == kActGeluTanh)
+    return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
   return g / (1.f + expf(-g)) * u;
 }
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.f + erff(v * 0.70710678118654752f)); }

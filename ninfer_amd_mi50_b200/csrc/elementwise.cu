@@ -489,7 +489,7 @@ extern "C" int nf_gated_bias_act(const void* gu, int in_dtype, const float* bias
                                  float limit, float alpha, int dtype, cudaStream_t stream) {
   if (M == 0) return 0;
   NF_REQUIRE(M > 0 && inner > 0 && M <= 65535 * 1024, "gated_bias_act: bad sizes M=%d inner=%d", M, inner);
-  NF_REQUIRE(kind == kActSilu || kind == kActCapped, "gated_bias_act: activation %d", kind);
+  NF_REQUIRE(kind == kActSilu || kind == kActCapped || kind == kActGeluTanh, "gated_bias_act: activation %d", kind);
   NF_REQUIRE(in_dtype == kF32 || in_dtype == dtype, "gated_bias_act: the input is float32 or of the output's type");
   // rows in grid.y, 65535 at a time
   for (int m0 = 0; m0 < M; m0 += 65535) {

@@ -123,7 +123,7 @@ using namespace nf;
 
 // C[M, N] = epilogue(A[M, K] * B[g]^T).  in_dtype: A and B; out_dtype: C (float32 allowed
 // with bfloat16 inputs, for logits).  groups == 1 and offsets == null: dense.
-// For swiglu (1: silu(gate) * up; 2: the capped form of common.cuh with act_limit, act_alpha),
+// For swiglu (1: silu(gate) * up; 2: the capped form of common.cuh with act_limit, act_alpha; 4: gelu_tanh(gate) * up),
 // B[g] has 2N rows (gate rows first) and C has N columns.
 extern "C" int nf_gemm_simt(const void* A, int lda, const void* B, long long b_group_stride, void* C,
                             int ldc, int M, int N, int K, int groups, int max_rows_per_group,
@@ -132,7 +132,7 @@ extern "C" int nf_gemm_simt(const void* A, int lda, const void* B, long long b_g
   if (M == 0 || N == 0) return 0;
   NF_REQUIRE(M > 0 && N > 0 && K > 0 && groups > 0 && a_div > 0, "gemm: bad sizes M=%d N=%d K=%d groups=%d", M, N, K, groups);
   NF_REQUIRE(groups == 1 || offsets, "gemm: grouped product needs row offsets");
-  NF_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm: epilogue %d (0 none, 1 silu-gated, 2 capped)", swiglu);
+  NF_REQUIRE((swiglu >= 0 && swiglu <= 2) || swiglu == kActGeluTanh, "gemm: epilogue %d (0 none, 1 silu-gated, 2 capped, 4 tanh-GELU-gated)", swiglu);
   const GatedActParams act{swiglu, act_limit, act_alpha};
   if (in_dtype == kF32 && out_dtype == kF32)
     return launch<float, float>(A, lda, B, (size_t)b_group_stride, C, ldc, M, N, K, groups, max_rows_per_group, offsets, a_rows, a_div, swiglu != 0, act, stream);

@@ -32,11 +32,11 @@ constexpr int kLaThreads = 128;
 __device__ __forceinline__ float la_act(float x, int use_silu) { return use_silu ? x / (1.f + expf(-x)) : x; }
 // One rotated pair of q and of k (already through `la_act`), by the angle pos * f, k scaled after
 // the turn.  The products are written out so that both kernels below round alike.
-__device__ __forceinline__ void la_turn(float q0, float q1, float k0, float k1, float angle, float k_scale, float& oq0,
-                                        float& oq1, float& ok0, float& ok1) {
+__device__ __forceinline__ void la_turn(float q0, float q1, float k0, float k1, float angle, float k_scale, float q_scale,
+                                        float& oq0, float& oq1, float& ok0, float& ok1) {
   const float cs = cosf(angle), sn = sinf(angle);
-  oq0 = __fsub_rn(__fmul_rn(q0, cs), __fmul_rn(q1, sn));
-  oq1 = __fadd_rn(__fmul_rn(q1, cs), __fmul_rn(q0, sn));
+  oq0 = __fmul_rn(__fsub_rn(__fmul_rn(q0, cs), __fmul_rn(q1, sn)), q_scale);      // (a scale of 1 changes no bit)
+  oq1 = __fmul_rn(__fadd_rn(__fmul_rn(q1, cs), __fmul_rn(q0, sn)), q_scale);
   ok0 = __fmul_rn(__fsub_rn(__fmul_rn(k0, cs), __fmul_rn(k1, sn)), k_scale);
   ok1 = __fmul_rn(__fadd_rn(__fmul_rn(k1, cs), __fmul_rn(k0, sn)), k_scale);
 }
@@ -46,8 +46,9 @@ __device__ __forceinline__ void la_turn(float q0, float q1, float k0, float k1, 
 // of a head; left to them, every one of them would repeat this work for the whole head.)
 template <typename T>
 __global__ void linear_attention_prepare_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0,
-                                                const float* __restrict__ inv_freq, int rot, float k_scale, int use_silu,
-                                                const int* __restrict__ positions, float* __restrict__ out, int H, int D) {
+                                                const float* __restrict__ inv_freq, int rot, float k_scale, float q_scale,
+                                                int use_silu, const int* __restrict__ positions, float* __restrict__ out,
+                                                int H, int D) {
   const int t = blockIdx.x;
   chain_wait(src);
   const int half = rot / 2, units = half + (D - rot);
@@ -61,26 +62,29 @@ __global__ void linear_attention_prepare_kernel(const T* __restrict__ src, int l
       float a, b, c, d;
       la_turn(la_act(to_float(row[q_col0 + base + u]), use_silu), la_act(to_float(row[q_col0 + base + u + half]), use_silu),
               la_act(to_float(row[k_col0 + base + u]), use_silu), la_act(to_float(row[k_col0 + base + u + half]), use_silu),
-              fpos * inv_freq[u], k_scale, a, b, c, d);
+              fpos * inv_freq[u], k_scale, q_scale, a, b, c, d);
       o[base + u] = a; o[base + u + half] = b;
       o[H * D + base + u] = c; o[H * D + base + u + half] = d;
     } else {
       const int i = rot + (u - half);
-      o[base + i] = la_act(to_float(row[q_col0 + base + i]), use_silu);
+      o[base + i] = __fmul_rn(la_act(to_float(row[q_col0 + base + i]), use_silu), q_scale);
       o[H * D + base + i] = __fmul_rn(la_act(to_float(row[k_col0 + base + i]), use_silu), k_scale);
     }
   }
 }
 
 // PREP: q and k come from `prepared` (float32, final; D a multiple of 4), four dimensions a copy.
-template <typename T, int EPL, int LANES, int CH, bool PREP>    // D <= LANES * EPL; CH tokens staged at a time
+// GATED: the decay is not a constant of the head but a number a (row, head), and so are a factor on
+// the row's k v^T and one on its output: S_t = a_t S_{t-1} + b_t k_t v_t^T, o_t = c_t S_t^T q_t, with
+// (a_t, b_t, c_t) at gates[(t * H + head) * 3] (what `mlstm_gates_kernel` below leaves).
+template <typename T, int EPL, int LANES, int CH, bool PREP, bool GATED>    // D <= LANES * EPL; CH tokens staged at a time
 __global__ void __launch_bounds__(kLaThreads)
 decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0, int v_col0,
                               const float* __restrict__ decay, const float* __restrict__ inv_freq, int rot,
-                              float k_scale, int use_silu, float* __restrict__ state, long slot_stride,
+                              float k_scale, float q_scale, int use_silu, float* __restrict__ state, long slot_stride,
                               const int* __restrict__ seg_row0, const int* __restrict__ seg_slot,
                               const int* __restrict__ seg_pos0, float* __restrict__ out, int H, int D, int V,
-                              const float* __restrict__ prepared) {
+                              const float* __restrict__ prepared, const float* __restrict__ gates) {
   constexpr int COLS = kLaThreads / LANES;                 // value columns a CTA
   constexpr bool VEC = EPL % 4 == 0;
   constexpr int PAD = VEC ? 4 : 0;
@@ -91,14 +95,15 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
   __shared__ __align__(16) float sq[CH][DP];
   __shared__ __align__(16) float sk[CH][DP];
   __shared__ float sv[CH][COLS];
+  __shared__ float sg[GATED ? CH : 1][3];
   const int seg = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * COLS;
   const int tid = threadIdx.x, lane = tid % LANES, cidx = tid / LANES, col = col0 + cidx;
   const bool live = col < V;
   chain_release_if_small();
-  chain_wait(src, state, prepared);
+  chain_wait(src, state, prepared, gates);
   const int row0 = seg_row0[seg], rows = seg_row0[seg + 1] - row0;
   const int pos0 = seg_pos0[seg];
-  const float g = decay[head];
+  const float g = GATED ? 0.f : decay[head];
   float* sp = state + (size_t)seg_slot[seg] * slot_stride + ((size_t)head * V + (live ? col : 0)) * D + lane * EPL;
   float s[EPL];
   const bool vec_state = VEC && D % 4 == 0 && (slot_stride % 4 == 0) && ((uintptr_t)state % 16 == 0);
@@ -123,7 +128,14 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
   constexpr int RP = PREP ? (CH * (DPAD / 4) + kLaThreads - 1) / kLaThreads : 1;
   T rq0[RRAW], rq1[RRAW], rk0[RRAW], rk1[RRAW], rv[VMAX];
   float4 fq[RP], fk[RP];
+  float rg[3] = {0.f, 0.f, 0.f};
   auto fetch = [&](int c0, int n) {
+    if constexpr (GATED) {
+      if (tid < n) {
+        const float* gp = gates + ((size_t)(row0 + c0 + tid) * H + head) * 3;
+        rg[0] = gp[0]; rg[1] = gp[1]; rg[2] = gp[2];
+      }
+    }
     if constexpr (PREP) {
 #pragma unroll
       for (int r = 0; r < RP; ++r) {
@@ -156,6 +168,9 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
     }
   };
   auto stage = [&](int c0, int n) {
+    if constexpr (GATED) {
+      if (tid < n) { sg[tid][0] = rg[0]; sg[tid][1] = rg[1]; sg[tid][2] = rg[2]; }
+    }
     if constexpr (PREP) {
 #pragma unroll
       for (int r = 0; r < RP; ++r) {
@@ -174,11 +189,11 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
           if (u < half) {
             float a, b, c, d;
             la_turn(la_act(to_float(rq0[r]), use_silu), la_act(to_float(rq1[r]), use_silu), la_act(to_float(rk0[r]), use_silu),
-                    la_act(to_float(rk1[r]), use_silu), (float)(pos0 + c0 + t) * inv_freq[u], k_scale, a, b, c, d);
+                    la_act(to_float(rk1[r]), use_silu), (float)(pos0 + c0 + t) * inv_freq[u], k_scale, q_scale, a, b, c, d);
             sq[t][at(u)] = a; sq[t][at(u + half)] = b;
             sk[t][at(u)] = c; sk[t][at(u + half)] = d;
           } else {
-            sq[t][at(i0)] = la_act(to_float(rq0[r]), use_silu);
+            sq[t][at(i0)] = __fmul_rn(la_act(to_float(rq0[r]), use_silu), q_scale);
             sk[t][at(i0)] = __fmul_rn(la_act(to_float(rk0[r]), use_silu), k_scale);
           }
         }
@@ -201,7 +216,9 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
     const float* qq0 = &sq[0][lane * (EPL + PAD)];
 #pragma unroll 2
     for (int t = 0; t < n; ++t) {
-      const float v = sv[t][cidx];
+      float v = sv[t][cidx];
+      float g_t = g;
+      if constexpr (GATED) { g_t = sg[t][0]; v *= sg[t][1]; }
       const float* kr = kq0 + t * DP;
       const float* qr = qq0 + t * DP;
       float o = 0.f;
@@ -210,20 +227,21 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
         for (int e = 0; e < EPL; e += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(kr + e);
           const float4 q4 = *reinterpret_cast<const float4*>(qr + e);
-          s[e] = fmaf(g, s[e], k4.x * v);         o = fmaf(s[e], q4.x, o);
-          s[e + 1] = fmaf(g, s[e + 1], k4.y * v); o = fmaf(s[e + 1], q4.y, o);
-          s[e + 2] = fmaf(g, s[e + 2], k4.z * v); o = fmaf(s[e + 2], q4.z, o);
-          s[e + 3] = fmaf(g, s[e + 3], k4.w * v); o = fmaf(s[e + 3], q4.w, o);
+          s[e] = fmaf(g_t, s[e], k4.x * v);         o = fmaf(s[e], q4.x, o);
+          s[e + 1] = fmaf(g_t, s[e + 1], k4.y * v); o = fmaf(s[e + 1], q4.y, o);
+          s[e + 2] = fmaf(g_t, s[e + 2], k4.z * v); o = fmaf(s[e + 2], q4.z, o);
+          s[e + 3] = fmaf(g_t, s[e + 3], k4.w * v); o = fmaf(s[e + 3], q4.w, o);
         }
       } else {
 #pragma unroll
         for (int e = 0; e < EPL; ++e) {
-          s[e] = fmaf(g, s[e], kr[e] * v);
+          s[e] = fmaf(g_t, s[e], kr[e] * v);
           o = fmaf(s[e], qr[e], o);
         }
       }
 #pragma unroll
       for (int w = LANES / 2; w > 0; w >>= 1) o += __shfl_xor_sync(0xffffffffu, o, w);
+      if constexpr (GATED) o *= sg[t][2];
       if (live && lane == 0) out[(size_t)(row0 + c0 + t) * H * V + (size_t)head * V + col] = o;
     }
   }
@@ -240,26 +258,98 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
   }
 }
 
+
+// The gates of a matrix-memory recurrence (mLSTM) with exponential gating, stabilised by a running
+// maximum, and its normaliser.  Per (request, head), from and into the request's state slot:
+//
+//   i_t = cap tanh((x_i + b_i) / cap)                     log input gate    (x_i, x_f: the row's gate projections)
+//   f_t = logsigmoid(cap tanh((x_f + b_f) / cap))         log forget gate
+//   m_t = max(f_t + m_{t-1}, i_t)                         (m starts at 0)
+//   a_t = exp(f_t + m_{t-1} - m_t),  b_t = exp(i_t - m_t)
+//   n_t = a_t n_{t-1} + b_t k_t                           (n starts at 0)
+//   c_t = 1 / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)        q_t = q * q_scale
+//
+// and leaves (a_t, b_t, c_t) at gates[(t * H + head) * 3], with which the recurrence kernel above runs
+// S_t = a_t S_{t-1} + b_t k_t v_t^T, o_t = c_t S_t^T q_t.  One warp a (request, head) walks the rows in
+// order; n lies in the lanes' registers (dimension lane + 32 j), m in every lane alike.  Everything is
+// float32; a row's numbers depend on earlier rows only through (n, m), which hold the same bits however
+// the request was cut.  cap <= 0: the gate projections enter uncapped.
+template <typename T>
+__global__ void __launch_bounds__(32)
+mlstm_gates_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0, float q_scale,
+                   const float* __restrict__ pre, int ldp, int i_col0, int f_col0, const float* __restrict__ bias_i,
+                   const float* __restrict__ bias_f, float cap, float* __restrict__ state_n,
+                   float* __restrict__ state_m, long slot_stride, const int* __restrict__ seg_row0,
+                   const int* __restrict__ seg_slot, float* __restrict__ gates, int H, int D) {
+  constexpr int NMAX = 8;                      // D <= 256
+  const int seg = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  chain_release_if_small();
+  chain_wait(src, pre, state_n, state_m);
+  const int row0 = seg_row0[seg], rows = seg_row0[seg + 1] - row0;
+  float* np = state_n + (size_t)seg_slot[seg] * slot_stride + (size_t)head * D;
+  float* mp = state_m + (size_t)seg_slot[seg] * slot_stride + head;
+  float n[NMAX];
+#pragma unroll
+  for (int j = 0; j < NMAX; ++j) n[j] = lane + 32 * j < D ? np[lane + 32 * j] : 0.f;
+  float m = *mp;
+  const float bi = bias_i ? bias_i[head] : 0.f, bf = bias_f ? bias_f[head] : 0.f;
+  for (int t = 0; t < rows; ++t) {
+    const size_t r = (size_t)(row0 + t);
+    float xi = pre[r * ldp + i_col0 + head] + bi, xf = pre[r * ldp + f_col0 + head] + bf;
+    if (cap > 0.f) { xi = cap * tanhf(xi / cap); xf = cap * tanhf(xf / cap); }
+    const float f = fminf(xf, 0.f) - log1pf(expf(-fabsf(xf)));
+    const float m_new = fmaxf(f + m, xi);
+    const float a = expf(f + m - m_new), b = expf(xi - m_new);
+    m = m_new;
+    const T* qr = src + r * ld + q_col0 + (size_t)head * D;
+    const T* kr = src + r * ld + k_col0 + (size_t)head * D;
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NMAX; ++j) {
+      const int d = lane + 32 * j;
+      if (d < D) {
+        n[j] = fmaf(a, n[j], b * to_float(kr[d]));
+        dot = fmaf(n[j], __fmul_rn(to_float(qr[d]), q_scale), dot);
+      }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) {
+      float* gp = gates + (r * H + head) * 3;
+      gp[0] = a; gp[1] = b;
+      gp[2] = 1.f / (fmaxf(fabsf(dot), expf(-m)) + 1e-6f);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NMAX; ++j)
+    if (lane + 32 * j < D) np[lane + 32 * j] = n[j];
+  if (lane == 0) *mp = m;
+}
+
 template <typename T, int EPL, int LANES, int CH, bool PREP>
 static void launch_la(const void* src, int ld, int q0, int k0, int v0, const float* decay, const float* inv_freq,
-                      int rot, float k_scale, int use_silu, float* state, long long slot_stride, const int* seg_row0,
-                      const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D, int V,
-                      const float* prepared, cudaStream_t stream) {
+                      int rot, float k_scale, float q_scale, int use_silu, float* state, long long slot_stride,
+                      const int* seg_row0, const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D,
+                      int V, const float* prepared, const float* gates, cudaStream_t stream) {
   constexpr int COLS = kLaThreads / LANES;
   dim3 grid(S, H, (V + COLS - 1) / COLS);
-  launch_chained(decay_linear_attention_kernel<T, EPL, LANES, CH, PREP>, grid, dim3(kLaThreads), 0, stream, (const T*)src, ld,
-                 q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, (long)slot_stride, seg_row0, seg_slot,
-                 seg_pos0, out, H, D, V, prepared);
+  if (gates)
+    launch_chained(decay_linear_attention_kernel<T, EPL, LANES, CH, PREP, true>, grid, dim3(kLaThreads), 0, stream, (const T*)src, ld,
+                   q0, k0, v0, decay, inv_freq, rot, k_scale, q_scale, use_silu, state, (long)slot_stride, seg_row0, seg_slot,
+                   seg_pos0, out, H, D, V, prepared, gates);
+  else
+    launch_chained(decay_linear_attention_kernel<T, EPL, LANES, CH, PREP, false>, grid, dim3(kLaThreads), 0, stream, (const T*)src, ld,
+                   q0, k0, v0, decay, inv_freq, rot, k_scale, q_scale, use_silu, state, (long)slot_stride, seg_row0, seg_slot,
+                   seg_pos0, out, H, D, V, prepared, gates);
 }
 
 template <typename T>
 static int dispatch_la(const void* src, int ld, int q0, int k0, int v0, const float* decay, const float* inv_freq,
-                       int rot, float k_scale, int use_silu, float* state, long long slot_stride, const int* seg_row0,
-                       const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D, int V,
-                       const float* prepared, int single, cudaStream_t stream) {
+                       int rot, float k_scale, float q_scale, int use_silu, float* state, long long slot_stride,
+                       const int* seg_row0, const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D,
+                       int V, const float* prepared, const float* gates, int single, cudaStream_t stream) {
 #define NF_LA(E, L, C, P)                                                                                          \
-  launch_la<T, E, L, C, P>(src, ld, q0, k0, v0, decay, inv_freq, rot, k_scale, use_silu, state, slot_stride, seg_row0, \
-                           seg_slot, seg_pos0, out, S, H, D, V, prepared, stream)
+  launch_la<T, E, L, C, P>(src, ld, q0, k0, v0, decay, inv_freq, rot, k_scale, q_scale, use_silu, state, slot_stride, \
+                           seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, gates, stream)
   // single: every segment brings one row (a decode step): one token staged at a time, few registers
   if (prepared) {
     if (D <= 32) NF_LA(4, 8, 16, true);
@@ -296,35 +386,56 @@ extern "C" int nf_decay_linear_attention_max_dim() { return 256; }
 // [H][V][D]; out float32 [T, H * V].  prepared: null, or what nf_linear_attention_prepare made of the
 // same rows (q and k are then taken from there as they are; D a multiple of 4 above 16).  single != 0:
 // every segment brings one row.
+// gates: null, or float32 [T, H, 3] of (decay, factor on k v^T, factor on the output) a (row, head), which
+// then stand in for `decay` (which may be null).  q_scale multiplies q after the turn, as k_scale does k.
 extern "C" int nf_decay_linear_attention(const void* src, int ld, int q_col0, int k_col0, int v_col0,
                                          const float* decay, const float* inv_freq, int rot, float k_scale,
                                          int use_silu, float* state, long long slot_stride, const int* seg_row0,
                                          const int* seg_slot, const int* seg_pos0, float* out, int S, int H, int D,
-                                         int V, int dtype, const float* prepared, int single, cudaStream_t stream) {
+                                         int V, int dtype, const float* prepared, int single, float q_scale,
+                                         const float* gates, cudaStream_t stream) {
   if (S == 0) return 0;
+  NF_REQUIRE(decay || gates, "linear attention: neither a decay a head nor gates a row");
   NF_REQUIRE(S > 0 && H > 0 && D > 0 && V > 0 && D <= 256, "linear attention: bad sizes S=%d H=%d D=%d V=%d", S, H, D, V);
   NF_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "linear attention: rot=%d with D=%d", rot, D);
   NF_REQUIRE(H <= 65535 && (V + 7) / 8 <= 65535, "linear attention: too many heads or columns");
   NF_REQUIRE(!prepared || (D % 4 == 0 && D > 16 && (uintptr_t)prepared % 16 == 0), "linear attention: prepared q and k need D a multiple of 4 above 16");
   if (dtype == kF32)
-    return dispatch_la<float>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, use_silu, state,
-                              slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, single, stream);
-  return dispatch_la<__nv_bfloat16>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, use_silu, state,
-                                    slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, single, stream);
+    return dispatch_la<float>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, q_scale, use_silu, state,
+                              slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, gates, single, stream);
+  return dispatch_la<__nv_bfloat16>(src, ld, q_col0, k_col0, v_col0, decay, inv_freq, rot, k_scale, q_scale, use_silu, state,
+                                    slot_stride, seg_row0, seg_slot, seg_pos0, out, S, H, D, V, prepared, gates, single, stream);
 }
 
 // out float32 [T, 2 H D]: q then k of every row, activated, turned by positions[t] and (k) scaled.
 extern "C" int nf_linear_attention_prepare(const void* src, int ld, int q_col0, int k_col0, const float* inv_freq, int rot,
                                            float k_scale, int use_silu, const int* positions, float* out, int T, int H,
-                                           int D, int dtype, cudaStream_t stream) {
+                                           int D, int dtype, float q_scale, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && H > 0 && D > 0 && rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq),
              "linear attention prepare: bad sizes T=%d H=%d D=%d rot=%d", T, H, D, rot);
   const int units = H * (rot / 2 + D - rot);
   const dim3 grid(T, (units + 1023) / 1024 < 1 ? 1 : (units + 1023) / 1024);
   if (dtype == kF32)
-    launch_chained(linear_attention_prepare_kernel<float>, grid, dim3(256), 0, stream, (const float*)src, ld, q_col0, k_col0, inv_freq, rot, k_scale, use_silu, positions, out, H, D);
+    launch_chained(linear_attention_prepare_kernel<float>, grid, dim3(256), 0, stream, (const float*)src, ld, q_col0, k_col0, inv_freq, rot, k_scale, q_scale, use_silu, positions, out, H, D);
   else
-    launch_chained(linear_attention_prepare_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)src, ld, q_col0, k_col0, inv_freq, rot, k_scale, use_silu, positions, out, H, D);
+    launch_chained(linear_attention_prepare_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)src, ld, q_col0, k_col0, inv_freq, rot, k_scale, q_scale, use_silu, positions, out, H, D);
   return check_launch("linear_attention_prepare");
+}
+
+// src [T, ld] holds q at q_col0 and k at k_col0 (H x D each, as the recurrence reads them); pre float32
+// [T, ldp] holds the gate projections of the H heads at i_col0 and f_col0; bias_i, bias_f float32 [H] or
+// null; state_n (slot s at + s * slot_stride: [H][D]) and state_m ([H]) float32; gates float32 [T, H, 3].
+extern "C" int nf_mlstm_gates(const void* src, int ld, int q_col0, int k_col0, float q_scale, const float* pre, int ldp,
+                              int i_col0, int f_col0, const float* bias_i, const float* bias_f, float cap,
+                              float* state_n, float* state_m, long long slot_stride, const int* seg_row0,
+                              const int* seg_slot, float* gates, int S, int H, int D, int dtype, cudaStream_t stream) {
+  if (S == 0) return 0;
+  NF_REQUIRE(S > 0 && H > 0 && H <= 65535 && D > 0 && D <= 256, "mlstm gates: bad sizes S=%d H=%d D=%d", S, H, D);
+  NF_REQUIRE(i_col0 >= 0 && f_col0 >= 0 && i_col0 + H <= ldp && f_col0 + H <= ldp, "mlstm gates: the gate columns leave their rows");
+  if (dtype == kF32)
+    launch_chained(mlstm_gates_kernel<float>, dim3(S, H), dim3(32), 0, stream, (const float*)src, ld, q_col0, k_col0, q_scale, pre, ldp, i_col0, f_col0, bias_i, bias_f, cap, state_n, state_m, (long)slot_stride, seg_row0, seg_slot, gates, H, D);
+  else
+    launch_chained(mlstm_gates_kernel<__nv_bfloat16>, dim3(S, H), dim3(32), 0, stream, (const __nv_bfloat16*)src, ld, q_col0, k_col0, q_scale, pre, ldp, i_col0, f_col0, bias_i, bias_f, cap, state_n, state_m, (long)slot_stride, seg_row0, seg_slot, gates, H, D);
+  return check_launch("mlstm_gates");
 }

@@ -57,6 +57,108 @@ qk_whole_norm_append_kernel(const float* __restrict__ proj, int ld, int q_col0, 
   }
 }
 
+
+// The same stage for an attention with values of their own and a rotation: biases; q and k each over
+// the root mean square of the WHOLE projection times a weight of the projection's width; then the first
+// `rot` dimensions of every q and k head turned by the row's position (pair (i, i + rot/2), angle
+// pos * inv_freq[i] in float32), cosine and sine both times `mag`; q goes out in the cache's type, the
+// key and the value (bias added) into the request's page.  Two page layouts:
+//   rows == 0: [2 (k, v)][kv_heads][page_size][D] (needs Dv == D), what the flash and decode kernels read;
+//   rows == 1: [page_size][kv_heads * D | kv_heads * Dv], one row a token, for key and value sizes that differ.
+// Hkv == 0: a layer that reads another layer's keys brings queries only.
+// The row's normed values wait in shared memory (float32) between the two passes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0, int k_col0, int v_col0,
+                              const float* __restrict__ bias_q, const float* __restrict__ bias_k,
+                              const float* __restrict__ bias_v, const float* __restrict__ wq,
+                              const float* __restrict__ wk, float eps, const float* __restrict__ inv_freq, int rot,
+                              float mag, const int* __restrict__ positions, const int* __restrict__ row_seg,
+                              T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv, T* __restrict__ pages,
+                              const int* __restrict__ block_table, int bt_width, int page_size, int num_pages,
+                              int rows_layout) {
+  extern __shared__ float y[];                 // [Hq * D + Hkv * D]
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  chain_release_if_small();
+  chain_wait(proj);
+  const float* row = proj + (size_t)t * ld;
+  const int QW = Hq * D, KW = Hkv * D;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < QW; i += blockDim.x) {
+    const float v = row[q_col0 + i] + (bias_q ? bias_q[i] : 0.f);
+    y[i] = v;
+    sq = fmaf(v, v, sq);
+  }
+  for (int i = threadIdx.x; i < KW; i += blockDim.x) {
+    const float v = row[k_col0 + i] + (bias_k ? bias_k[i] : 0.f);
+    y[QW + i] = v;
+    sk = fmaf(v, v, sk);
+  }
+  const float inv_q = 1.f / sqrtf(block_sum(sq, red) / (float)QW + eps);
+  const float inv_k = KW ? 1.f / sqrtf(block_sum(sk, red) / (float)KW + eps) : 0.f;
+  for (int i = threadIdx.x; i < QW; i += blockDim.x) y[i] = y[i] * inv_q * wq[i];
+  for (int i = threadIdx.x; i < KW; i += blockDim.x) y[QW + i] = y[QW + i] * inv_k * wk[i];
+  __syncthreads();
+  const int pos = positions[t];
+  const float fpos = (float)pos;
+  const int half = rot / 2;
+  T* krow = nullptr;                           // where head 0's key of this token starts
+  size_t k_head_stride = 0, v_head_stride = 0;
+  T* vrow = nullptr;
+  if (Hkv > 0) {
+    const int lp = pos / page_size;
+    const int page = (lp >= 0 && lp < bt_width) ? block_table[(size_t)row_seg[t] * bt_width + lp] : -1;
+    if (page >= 0 && page < num_pages) {       // no page reserved: never write out of bounds
+      const int in_page = pos - lp * page_size;
+      if (rows_layout) {
+        krow = pages + ((size_t)page * page_size + in_page) * ((size_t)Hkv * (D + Dv));
+        vrow = krow + (size_t)Hkv * D;
+        k_head_stride = D; v_head_stride = Dv;
+      } else {
+        krow = pages + ((size_t)page * 2 * Hkv * page_size + in_page) * D;
+        k_head_stride = v_head_stride = (size_t)page_size * D;
+        vrow = krow + (size_t)Hkv * k_head_stride;
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < QW + KW; i += blockDim.x) {
+    const bool is_q = i < QW;
+    const int c = is_q ? i : i - QW;
+    const int head = c / D, d = c - head * D;
+    float v = y[i];
+    if (d < rot) {
+      const int u = d < half ? d : d - half;
+      const float other = y[d < half ? i + half : i - half];
+      float sn, cs;
+      sincosf(fpos * inv_freq[u], &sn, &cs);
+      sn *= mag; cs *= mag;
+      v = d < half ? v * cs - other * sn : v * cs + other * sn;
+    }
+    if (is_q) q_out[(size_t)t * QW + c] = from_float<T>(v);
+    else if (krow) krow[(size_t)head * k_head_stride + d] = from_float<T>(v);
+  }
+  if (vrow) {
+    for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
+      const int head = i / Dv, d = i - head * Dv;
+      vrow[(size_t)head * v_head_stride + d] = from_float<T>(row[v_col0 + i] + (bias_v ? bias_v[i] : 0.f));
+    }
+  }
+}
+
+// out[t, c] = o[t, c] * sigmoid(g[t, g_col0 + c]): an output gate element by element; the gate's
+// logits are float32 sums or of the rows' type.
+template <typename T, typename TG>
+__global__ void sigmoid_gate_rows_kernel(const T* __restrict__ o, const TG* __restrict__ g, int ldg, int g_col0,
+                                         T* __restrict__ out, int width) {
+  const int t = blockIdx.y;
+  chain_wait(o, g);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const float gv = to_float(g[(size_t)t * ldg + g_col0 + c]);
+  out[(size_t)t * width + c] = from_float<T>(to_float(o[(size_t)t * width + c]) * (1.f / (1.f + expf(-gv))));
+}
+
 }  // namespace nf
 
 using namespace nf;
@@ -75,4 +177,53 @@ extern "C" int nf_qk_whole_norm_append(const float* proj, int ld, int q_col0, in
   else
     launch_chained(qk_whole_norm_append_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, proj, ld, q_col0, k_col0, bias_q, bias_k, wq, wk, eps, positions, row_seg, (__nv_bfloat16*)q_out, Hq, Hkv, D, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, append);
   return check_launch("qk_whole_norm_append");
+}
+
+// proj float32 [T, ld]: q (Hq x D) at q_col0, and with Hkv > 0 k (Hkv x D) at k_col0 and v (Hkv x Dv) at
+// v_col0.  rows_layout 0: pages [.., 2, Hkv, page_size, D] (Dv == D); 1: pages [.., page_size, Hkv * (D + Dv)].
+extern "C" int nf_whole_norm_rope_append(const float* proj, int ld, int q_col0, int k_col0, int v_col0,
+                                         const float* bias_q, const float* bias_k, const float* bias_v,
+                                         const float* wq, const float* wk, float eps, const float* inv_freq, int rot,
+                                         float mag, const int* positions, const int* row_seg, void* q_out, int T,
+                                         int Hq, int Hkv, int D, int Dv, void* pages, const int* block_table,
+                                         int bt_width, int page_size, int num_pages, int rows_layout, int dtype,
+                                         cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && Hq > 0 && Hkv >= 0 && D > 0 && Dv > 0 && wq && (Hkv == 0 || wk), "whole_norm_rope_append: bad arguments");
+  NF_REQUIRE(q_col0 >= 0 && q_col0 + Hq * D <= ld, "whole_norm_rope_append: the queries leave the projection");
+  NF_REQUIRE(Hkv == 0 || (k_col0 >= 0 && v_col0 >= 0 && k_col0 + Hkv * D <= ld && v_col0 + Hkv * Dv <= ld),
+             "whole_norm_rope_append: keys or values leave the projection");
+  NF_REQUIRE(Hkv == 0 || (pages && block_table), "whole_norm_rope_append: keys without a cache");
+  NF_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "whole_norm_rope_append: %d turned dimensions of %d", rot, D);
+  NF_REQUIRE(rows_layout || Hkv == 0 || D == Dv, "whole_norm_rope_append: the head-major page needs equal key and value sizes");
+  const size_t smem = (size_t)(Hq + Hkv) * D * sizeof(float);
+  NF_REQUIRE(smem <= 200 * 1024, "whole_norm_rope_append: %d values a row do not fit shared memory", (Hq + Hkv) * D);
+  if (dtype == kF32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(whole_norm_rope_append_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_chained(whole_norm_rope_append_kernel<float>, dim3(T), dim3(256), smem, stream, proj, ld, q_col0, k_col0, v_col0, bias_q, bias_k, bias_v, wq, wk, eps, inv_freq, rot, mag, positions, row_seg, (float*)q_out, Hq, Hkv, D, Dv, (float*)pages, block_table, bt_width, page_size, num_pages, rows_layout);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(whole_norm_rope_append_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_chained(whole_norm_rope_append_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, proj, ld, q_col0, k_col0, v_col0, bias_q, bias_k, bias_v, wq, wk, eps, inv_freq, rot, mag, positions, row_seg, (__nv_bfloat16*)q_out, Hq, Hkv, D, Dv, (__nv_bfloat16*)pages, block_table, bt_width, page_size, num_pages, rows_layout);
+  }
+  return check_launch("whole_norm_rope_append");
+}
+
+// o, out [T, width] of `dtype`; g [T, ldg] float32 (g_dtype 0) or of `dtype`.
+extern "C" int nf_sigmoid_gate_rows(const void* o, const void* g, int g_dtype, int ldg, int g_col0, void* out, int T,
+                                    int width, int dtype, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && T <= 65535 * 1024 && width > 0 && g_col0 >= 0 && g_col0 + width <= ldg, "sigmoid_gate_rows: bad sizes");
+  NF_REQUIRE(g_dtype == kF32 || g_dtype == dtype, "sigmoid_gate_rows: the gate is float32 or of the rows' type");
+  for (int t0 = 0; t0 < T; t0 += 65535) {
+    const int rows = T - t0 < 65535 ? T - t0 : 65535;
+    const dim3 grid((width + 255) / 256, rows);
+    const size_t off = (size_t)t0 * width, goff = (size_t)t0 * ldg;
+    if (dtype == kF32)
+      launch_chained(sigmoid_gate_rows_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)o + off, (const float*)g + goff, ldg, g_col0, (float*)out + off, width);
+    else if (g_dtype == kF32)
+      launch_chained(sigmoid_gate_rows_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)o + off, (const float*)g + goff, ldg, g_col0, (__nv_bfloat16*)out + off, width);
+    else
+      launch_chained(sigmoid_gate_rows_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)o + off, (const __nv_bfloat16*)g + goff, ldg, g_col0, (__nv_bfloat16*)out + off, width);
+  }
+  return check_launch("sigmoid_gate_rows");
 }

@@ -58,6 +58,34 @@ router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp
                topk_idx, topk_w, extra_out, lane);
 }
 
+__global__ void __launch_bounds__(128)
+router_select_ruled_kernel(const float* __restrict__ logits, int n_tokens, int E, int k,
+                           const float* __restrict__ correction, int n_groups, int keep, float out_scale,
+                           int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  extern __shared__ float smem[];      // [4 warps][2 E + n_groups]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  chain_wait(logits);
+  if (t >= n_tokens) return;
+  float* base = smem + (size_t)warp * (2 * E + n_groups);
+  select_token_ruled(logits + (size_t)t * E, base, base + E, base + 2 * E, t, E, k, correction, n_groups, keep,
+                     out_scale, topk_idx, topk_w, lane);
+}
+
+// Experts that have no matrices because their output is their input: y[p] = x[order[p] / k] for the sorted
+// pairs p from offsets[first] on (the pairs of the experts from `first` up), in pieces of 16, 4 or 2 bytes.
+template <typename U>
+__global__ void identity_expert_rows_kernel(const U* __restrict__ x, const int* __restrict__ order, int k,
+                                            const int* __restrict__ offsets, int first, U* __restrict__ y,
+                                            int pieces) {
+  const int p = blockIdx.x;
+  chain_wait(x, order, offsets, y);
+  if (p < offsets[first]) return;
+  const U* src = x + (size_t)(order[p] / k) * pieces;
+  U* dst = y + (size_t)p * pieces;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) dst[i] = src[i];
+}
+
 template <bool STAGED>
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ topk_idx, int n, int E, int* __restrict__ offsets,
@@ -552,4 +580,46 @@ extern "C" int nf_moe_plan(const int* topk_idx, int n, int E, int* offsets, int*
     moe_plan_kernel<false><<<1, 1024, (E + 1) * sizeof(int), stream>>>(topk_idx, n, E, offsets, order, inv, active, n_active_max);
   }
   return check_launch("moe_plan");
+}
+
+// logits[t, r] = x[t] . wr[r], float32, for the `rows` rows of wr: the router's products alone.
+extern "C" int nf_router_logits(const void* x, const float* wr, int T, int hidden, int rows, float* logits, int dtype,
+                                cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && hidden > 0 && rows > 0, "router logits: bad sizes T=%d hidden=%d rows=%d", T, hidden, rows);
+  NF_REQUIRE((size_t)hidden * 4 <= 200 * 1024, "router: hidden=%d needs more shared memory than a block has", hidden);
+  if (dtype == kF32) return launch_logits_t<float>(x, wr, T, hidden, rows, logits, stream);
+  return launch_logits_t<__nv_bfloat16>(x, wr, T, hidden, rows, logits, stream);
+}
+
+// Selection by `select_token_ruled` over logits float32 [T, E] (correction float32 [E] or null; n_groups 0:
+// no groups) -> topk_idx int32 [T, k], topk_w float32 [T, k].
+extern "C" int nf_router_select_ruled(const float* logits, int T, int E, int k, const float* correction, int n_groups,
+                                      int keep, float out_scale, int* topk_idx, float* topk_w, cudaStream_t stream) {
+  if (T == 0) return 0;
+  NF_REQUIRE(T > 0 && E > 0 && k > 0 && k <= E, "router: bad sizes T=%d E=%d k=%d", T, E, k);
+  NF_REQUIRE(n_groups >= 0 && (n_groups == 0 || (E % n_groups == 0 && keep >= 1 && keep <= n_groups && (E / n_groups) * keep >= k)),
+             "router: %d experts in %d groups of which %d are kept cannot give %d choices", E, n_groups, keep, k);
+  const size_t smem = (size_t)4 * (2 * E + n_groups) * sizeof(float);
+  NF_REQUIRE(smem <= 48 * 1024, "router: %d experts are more than the selection kernel holds", E);
+  launch_chained(router_select_ruled_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, logits, T, E, k, correction, n_groups, keep, out_scale, topk_idx, topk_w);
+  return check_launch("router_select_ruled");
+}
+
+// y [n_pairs, row_bytes]: the rows of the sorted pairs from offsets[first] on become copies of their tokens' rows of x.
+extern "C" int nf_identity_expert_rows(const void* x, const int* order, int k, const int* offsets, int first, void* y,
+                                       int n_pairs, int row_bytes, cudaStream_t stream) {
+  if (n_pairs == 0) return 0;
+  NF_REQUIRE(n_pairs > 0 && k > 0 && first >= 0 && row_bytes > 0 && row_bytes % 2 == 0, "identity_expert_rows: rows of %d bytes", row_bytes);
+  const bool wide = row_bytes % 16 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+  const int unit = wide ? 16 : (row_bytes % 4 == 0 ? 4 : 2);
+  const int pieces = row_bytes / unit;
+  const dim3 block(pieces >= 256 ? 256 : (pieces >= 64 ? 64 : 32));
+  if (unit == 16)
+    launch_chained(identity_expert_rows_kernel<uint4>, dim3(n_pairs), block, 0, stream, (const uint4*)x, order, k, offsets, first, (uint4*)y, pieces);
+  else if (unit == 4)
+    launch_chained(identity_expert_rows_kernel<unsigned>, dim3(n_pairs), block, 0, stream, (const unsigned*)x, order, k, offsets, first, (unsigned*)y, pieces);
+  else
+    launch_chained(identity_expert_rows_kernel<unsigned short>, dim3(n_pairs), block, 0, stream, (const unsigned short*)x, order, k, offsets, first, (unsigned short*)y, pieces);
+  return check_launch("identity_expert_rows");
 }

@@ -138,6 +138,102 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
   __syncwarp();
 }
 
+// One warp, one token, with further rules of choice.  Scores s = softmax over all E logits.  The choice
+// scores are s + correction (if given); the weights use s without it.  With n_groups > 0 the experts
+// form n_groups equal groups of neighbours, a group scores as its largest choice score, and only experts
+// of the `keep` best groups can be chosen (the others count as minus infinity: choice scores may be
+// negative).  The k largest choice scores are taken (ties to the lower index); their weights are
+// s_e / (sum of the chosen s + 1e-20) * out_scale.  `sc`, `ch`: E floats each, `gs`: n_groups floats of
+// the warp's shared memory; logits[t, e] sits at row[e].  A logit that is not a number makes the
+// row's weights NaN and never an index.
+__device__ __forceinline__ void select_token_ruled(const float* __restrict__ row, float* sc, float* ch, float* gs,
+                                                   int t, int E, int k, const float* __restrict__ correction,
+                                                   int n_groups, int keep, float out_scale,
+                                                   int* __restrict__ topk_idx, float* __restrict__ topk_w, int lane) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) {
+    const float v = row[e];
+    sc[e] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = warp_max(mx);
+  bool bad = false;
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    float p = expf(sc[e] - mx);
+    if (!(p >= 0.f && p <= 1.f)) { p = 0.f; bad = true; }
+    sc[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  bad = __any_sync(0xffffffffu, bad) || !(sum > 0.f);
+  if (bad) sum = 1.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = sc[e] / sum;
+    sc[e] = p;
+    ch[e] = p + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (n_groups > 0) {
+    const int per = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float b = -INFINITY;
+      for (int j = 0; j < per; ++j) b = fmaxf(b, ch[g * per + j]);
+      gs[g] = b;
+    }
+    __syncwarp();
+    // the `keep` best groups are marked by +infinity in gs; the others' experts are taken out
+    for (int r = 0; r < keep; ++r) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || best_g == 0x7fffffff)) { best = v; best_g = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) { best = ob; best_g = og; }
+      }
+      if (lane == 0 && best_g != 0x7fffffff) gs[best_g] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / per] != INFINITY) ch[e] = -INFINITY;
+    __syncwarp();
+  }
+  float sel_sum = 0.f;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float c = ch[e];
+      // (taken ones hold NaN and lose every comparison; the first open expert stands in if all are -inf)
+      if (c > best || (best_e == 0x7fffffff && c == c)) { best = c; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
+    }
+    if (best_e == 0x7fffffff) best_e = 0;            // cannot happen while k <= E
+    const float w = sc[best_e];
+    sel_sum += w;
+    __syncwarp();
+    if (lane == 0) {
+      topk_idx[(size_t)t * k + j] = best_e;
+      topk_w[(size_t)t * k + j] = w;
+      ch[best_e] = __int_as_float(0x7fc00000);       // taken
+    }
+    __syncwarp();
+  }
+  const float mul = bad ? __int_as_float(0x7fc00000) : out_scale / (sel_sum + 1e-20f);
+  for (int j = lane; j < k; j += 32) topk_w[(size_t)t * k + j] *= mul;
+  __syncwarp();
+}
+
 // Plan by one block: stable counting sort of the n pairs by expert, and (if `active` is
 // given) the list of experts that have pairs, ascending, padded with -1 to n_active_max.  `counts` is E + 1 ints
 // of shared memory; with STAGED, `ex` holds n 16-bit expert ids so that the E passes over the

@@ -414,7 +414,7 @@ extern "C" int nf_skinny_gemm(const void* X, int ldx, const void* W, long long w
   const size_t wgs = (size_t)w_group_stride;
   if (swiglu) {
     NF_REQUIRE(out_dtype == kBF16, "skinny_gemm: the SwiGLU epilogue writes bfloat16");
-    NF_REQUIRE(swiglu == kActSilu || swiglu == kActCapped, "skinny_gemm: gated epilogue %d", swiglu);
+    NF_REQUIRE(swiglu == kActSilu || swiglu == kActCapped || swiglu == kActGeluTanh, "skinny_gemm: gated epilogue %d", swiglu);
     t_gated_act = GatedActParams{swiglu, act_limit, act_alpha};
     return launch_sw<true, __nv_bfloat16>(nt, packed != 0, X, ldx, W, wgs, Y, ldy, M, N, K, groups, max_rows, offsets, x_rows, x_div, group_map, n_mapped, early_index, stream);
   }

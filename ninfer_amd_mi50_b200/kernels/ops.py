@@ -143,6 +143,9 @@ def capped_activation(limit: float, alpha: float) -> Tuple[int, float, float]:
     return (2, float(limit), float(alpha))
 
 
+ACT_GELU_TANH = (4, 0.0, 0.0)     # gelu_tanh(gate) * up, gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+
+
 def _act(swiglu, act) -> Tuple[int, float, float]:
     """The epilogue a product is launched with: none, or the gated activation `act`."""
     if not swiglu:
@@ -377,8 +380,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return out
 
 
-def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    """x [M, K], w [2I, K] (gate rows first) -> silu(x gate^T) * (x up^T)  [M, I]."""
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act=None) -> torch.Tensor:
+    """x [M, K], w [2I, K] (gate rows first) -> silu(x gate^T) * (x up^T)  [M, I]; `act`: another gated
+    activation in silu's place (the product kernels' epilogues take it; after a library product it is a
+    pass of its own)."""
     _chk(x, "x"); _chk(w_gate_up, "w_gate_up", x.dtype)
     M, K = x.shape
     inner = w_gate_up.shape[0] // 2
@@ -386,12 +391,13 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         return torch.empty((M, inner), dtype=x.dtype, device=x.device)
     path = "simt" if x.dtype == torch.float32 else _bf16_path(M, K, "bf16_linear")
     if path == "large":
-        return silu_mul(torch.mm(x, w_gate_up.t()))
+        gu = torch.mm(x, w_gate_up.t())
+        return silu_mul(gu) if act is None else gated_bias_act(gu, None, act, x.dtype)
     out = torch.empty((M, inner), dtype=x.dtype, device=x.device)
     if path == "skinny":
-        _skinny(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True)
+        _skinny(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True, act=act)
     else:
-        _gemm_simt(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True)
+        _gemm_simt(x, K, w_gate_up, 0, out, M, inner, K, 1, M, None, None, 1, True, act=act)
     return out
 
 
@@ -567,6 +573,48 @@ def qk_whole_norm_append(proj: torch.Tensor, q_col0: int, k_col0: int, bias_q: O
               c_int(Hkv), c_int(D), _p(pages), _p(block_table), c_int(block_table.shape[1]), c_int(page_size),
               c_int(pages.shape[0]), c_int(1 if append else 0), c_int(_dt(pages)), _stream())
     return q
+
+
+def whole_norm_rope_append(proj: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, bias_q: Optional[torch.Tensor],
+                           bias_k: Optional[torch.Tensor], bias_v: Optional[torch.Tensor], wq: torch.Tensor,
+                           wk: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot: int,
+                           magnitude: float, Hq: int, Hkv: int, D: int, Dv: int, ctx, pages: Optional[torch.Tensor],
+                           block_table: Optional[torch.Tensor], page_size: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """proj float32 [T, ld] holds q (Hq x D) at q_col0 and, with Hkv > 0, k (Hkv x D) at k_col0 and v (Hkv x Dv)
+    at v_col0.  Adds the biases; q and k each over the root mean square of their whole row slice, times wq / wk
+    (of the slice's width); the first `rot` dimensions of every q and k head turned by the row's position (pairs
+    (i, i + rot/2), inv_freq float32 [rot / 2]), cosine and sine times `magnitude`.  Returns q [T, Hq * D] in
+    `out_dtype` and writes key and value at (request, position): into pages [n, 2, Hkv, page_size, D] (then
+    Dv == D) or, when `pages` has three dimensions, into rows [n, page_size, Hkv * (D + Dv)].  Hkv = 0: the
+    queries alone."""
+    _chk(proj, "proj", torch.float32); _chk(wq, "wq", torch.float32)
+    for b, n in ((bias_q, "bias_q"), (bias_k, "bias_k"), (bias_v, "bias_v"), (wk, "wk"), (inv_freq, "inv_freq")):
+        if b is not None:
+            _chk(b, n, torch.float32)
+    T = proj.shape[0]
+    q = torch.empty((T, Hq * D), dtype=out_dtype, device=proj.device)
+    rows_layout = 0
+    if Hkv:
+        _chk(pages, "pages", out_dtype); _chk(block_table, "block_table", torch.int32)
+        rows_layout = 1 if pages.dim() == 3 else 0
+    _lib.call("nf_whole_norm_rope_append", _p(proj), c_int(proj.shape[1]), c_int(q_col0), c_int(k_col0), c_int(v_col0),
+              _p(bias_q), _p(bias_k), _p(bias_v), _p(wq), _p(wk), c_float(eps), _p(inv_freq) if rot else None, c_int(rot),
+              c_float(magnitude), _p(ctx.positions), _p(ctx.row_seg), _p(q), c_int(T), c_int(Hq), c_int(Hkv), c_int(D),
+              c_int(Dv), _p(pages) if Hkv else None, _p(block_table) if Hkv else None,
+              c_int(block_table.shape[1] if Hkv else 0), c_int(page_size), c_int(pages.shape[0] if Hkv else 0),
+              c_int(rows_layout), c_int(_dt(q)), _stream())
+    return q
+
+
+def sigmoid_gate_rows(o: torch.Tensor, g_src: torch.Tensor, g_col0: int) -> torch.Tensor:
+    """o [T, n] times sigmoid(g_src[:, g_col0 : g_col0 + n]) element by element; the gate's logits are float32
+    or of o's type."""
+    _chk(o, "o"); _chk(g_src, "g_src")
+    T, n = o.shape
+    out = torch.empty_like(o)
+    _lib.call("nf_sigmoid_gate_rows", _p(o), _p(g_src), c_int(_dt(g_src)), c_int(g_src.shape[1]), c_int(g_col0), _p(out),
+              c_int(T), c_int(n), c_int(_dt(o)), _stream())
+    return out
 
 
 def biased_window_attention(q: torch.Tensor, Hq: int, Hkv: int, D: int, pages: torch.Tensor, block_table: torch.Tensor,
@@ -746,6 +794,46 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
               c_int(_route_flags(norm_topk, scoring)), _p(logits), _p(idx), _p(wts), _p(ext), _p(offsets), _p(order),
               _p(inv), _p(active), c_int(active.numel()), _p(_TICKETS[key]), c_int(_dt(x)), _stream())
     return idx, wts, ext, MoePlan(offsets, order, inv, E, T, k, active)
+
+
+def route_ruled(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, correction: Optional[torch.Tensor],
+                groups: int, keep: int, scale: float, real_experts: Optional[int] = None):
+    """Routing with rules of choice -> (idx int32 [T, k], weights float32 [T, k], plan over all E experts, plan of
+    the experts that have matrices).  Scores are the softmax of the float32 logits over all E experts; the choice
+    uses score + `correction` (float32 [E] or None) and, with `groups` > 0, only experts of the `keep` groups (of
+    `groups` equal groups of neighbours) whose best choice score is largest; the weights are the chosen experts'
+    scores (without the correction) over their sum (+ 1e-20), times `scale`.  The experts from `real_experts` up
+    (default: none) have no matrices - their output is their input, which `identity_expert_rows` fills in - so the
+    second plan shares the first one's arrays and stops at `real_experts`."""
+    _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
+    if correction is not None:
+        _chk(correction, "correction", torch.float32)
+    T, H = x.shape
+    if w_router.shape != (E, H):
+        raise ValueError("route_ruled: the routing matrix does not match the experts")
+    dev = x.device
+    logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+    idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+    wts = torch.empty((T, k), dtype=torch.float32, device=dev)
+    if T:
+        _lib.call("nf_router_logits", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), _p(logits), c_int(_dt(x)), _stream())
+        _lib.call("nf_router_select_ruled", _p(logits), c_int(T), c_int(E), c_int(k), _p(correction), c_int(groups),
+                  c_int(keep), c_float(scale), _p(idx), _p(wts), _stream())
+    plan = moe_plan(idx, E)
+    real = E if real_experts is None else int(real_experts)
+    if real == E:
+        return idx, wts, plan, plan
+    active = torch.where(plan.active < real, plan.active, torch.full_like(plan.active, -1)) if plan.active is not None else None
+    return idx, wts, plan, MoePlan(plan.offsets, plan.order, plan.inv, real, T, k, active)
+
+
+def identity_expert_rows(x: torch.Tensor, plan: MoePlan, k: int, first: int, y: torch.Tensor) -> None:
+    """The experts from `first` up return their input: rows of `y` [T * k, H] (sorted pairs) that belong to them
+    become copies of their tokens' rows of `x`."""
+    _chk(x, "x"); _chk(y, "y", x.dtype)
+    if y.shape[0]:
+        _lib.call("nf_identity_expert_rows", _p(x), _p(plan.order), c_int(k), _p(plan.offsets), c_int(first), _p(y),
+                  c_int(y.shape[0]), c_int(x.shape[1] * x.element_size()), _stream())
 
 
 def moe_uses_gathered_rows(x: torch.Tensor, w13) -> bool:
@@ -1244,13 +1332,19 @@ LINEAR_ATTENTION_MAX_DIM = 256
 
 def decay_linear_attention(src: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, decay: torch.Tensor,
                            inv_freq: Optional[torch.Tensor], rot: int, k_scale: float, silu: bool,
-                           state: torch.Tensor, ctx, heads: int, D: int, V: int) -> torch.Tensor:
+                           state: torch.Tensor, ctx, heads: int, D: int, V: int, q_scale: float = 1.0,
+                           gates: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The recurrence S <- decay_h S + k v^T, o = S^T q over a step's rows, request by request, from and into
     each request's state (float32 [slots, heads * V * D], a column's D entries contiguous).  q, k (heads x D) and
     v (heads x V) are columns of `src`; `silu` passes all three through SiLU first; the first `rot` dimensions of
-    every q and k head are turned by the row's position (inv_freq float32 [rot / 2]); k is scaled by `k_scale`.
-    Returns o float32 [T, heads * V]."""
-    _chk(src, "src"); _chk(decay, "decay", torch.float32); _chk(state, "state", torch.float32)
+    every q and k head are turned by the row's position (inv_freq float32 [rot / 2]); k is scaled by `k_scale`, q by
+    `q_scale`.  With `gates` (float32 [T, heads, 3] of (a, b, c) a row and head; `decay` may then be None) the
+    recurrence is S <- a S + b k v^T, o = c S^T q.  Returns o float32 [T, heads * V]."""
+    _chk(src, "src"); _chk(state, "state", torch.float32)
+    if gates is not None:
+        _chk(gates, "gates", torch.float32)
+    else:
+        _chk(decay, "decay", torch.float32)
     if rot:
         _chk(inv_freq, "inv_freq", torch.float32)
     T = src.shape[0]
@@ -1263,12 +1357,36 @@ def decay_linear_attention(src: torch.Tensor, q_col0: int, k_col0: int, v_col0: 
         prepared = torch.empty((T, 2 * heads * D), dtype=torch.float32, device=src.device)
         _lib.call("nf_linear_attention_prepare", _p(src), c_int(src.shape[1]), c_int(q_col0), c_int(k_col0),
                   _p(inv_freq) if rot else None, c_int(rot), c_float(k_scale), c_int(1 if silu else 0), _p(ctx.positions),
-                  _p(prepared), c_int(T), c_int(heads), c_int(D), c_int(_dt(src)), _stream())
+                  _p(prepared), c_int(T), c_int(heads), c_int(D), c_int(_dt(src)), c_float(q_scale), _stream())
     _lib.call("nf_decay_linear_attention", _p(src), c_int(src.shape[1]), c_int(q_col0), c_int(k_col0), c_int(v_col0),
               _p(decay), _p(inv_freq) if rot else None, c_int(rot), c_float(k_scale), c_int(1 if silu else 0),
               _p(state), c_longlong(state.stride(0)), _p(ctx.seg_row0), _p(ctx.seg_slot), _p(ctx.seg_pos0), _p(out),
-              c_int(ctx.S), c_int(heads), c_int(D), c_int(V), c_int(_dt(src)), _p(prepared), c_int(1 if single else 0), _stream())
+              c_int(ctx.S), c_int(heads), c_int(D), c_int(V), c_int(_dt(src)), _p(prepared), c_int(1 if single else 0),
+              c_float(q_scale), _p(gates), _stream())
     return out
+
+
+def mlstm_gates(src: torch.Tensor, q_col0: int, k_col0: int, q_scale: float, pre: torch.Tensor, i_col0: int, f_col0: int,
+                bias_i: Optional[torch.Tensor], bias_f: Optional[torch.Tensor], cap: float, state: torch.Tensor,
+                n_off: int, m_off: int, ctx, heads: int, D: int) -> torch.Tensor:
+    """The gates of the matrix-memory recurrence with a running maximum, request by request from and into each
+    request's state: log input gate i = cap tanh((pre_i + bias_i) / cap), log forget gate
+    f = logsigmoid(cap tanh((pre_f + bias_f) / cap)), m <- max(f + m, i), a = exp(f + m_old - m), b = exp(i - m),
+    n <- a n + b k, c = 1 / (max(|n . q q_scale|, exp(-m)) + 1e-6).  `pre` float32 [T, ld] holds the heads' gate
+    projections at i_col0 and f_col0; q and k (heads x D) are columns of `src`; a slot of `state` (float32
+    [slots, n]) keeps n at n_off ([heads][D]) and m at m_off ([heads]).  Returns float32 [T, heads, 3] of (a, b, c)
+    for `decay_linear_attention(..., gates=)`."""
+    _chk(src, "src"); _chk(pre, "pre", torch.float32); _chk(state, "state", torch.float32)
+    for b, n in ((bias_i, "bias_i"), (bias_f, "bias_f")):
+        if b is not None:
+            _chk(b, n, torch.float32)
+    T = src.shape[0]
+    gates = torch.empty((T, heads, 3), dtype=torch.float32, device=src.device)
+    _lib.call("nf_mlstm_gates", _p(src), c_int(src.shape[1]), c_int(q_col0), c_int(k_col0), c_float(q_scale), _p(pre),
+              c_int(pre.shape[1]), c_int(i_col0), c_int(f_col0), _p(bias_i), _p(bias_f), c_float(cap),
+              c_void_p(state.data_ptr() + 4 * n_off), c_void_p(state.data_ptr() + 4 * m_off), c_longlong(state.stride(0)),
+              _p(ctx.seg_row0), _p(ctx.seg_slot), _p(gates), c_int(ctx.S), c_int(heads), c_int(D), c_int(_dt(src)), _stream())
+    return gates
 
 
 # ---------------------------------------------------------------------------------------

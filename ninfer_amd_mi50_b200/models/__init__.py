@@ -1,1 +1,1 @@
-from . import qwen2_moe, vekasun, difavik, fetezen  # noqa: F401  (registration)
+from . import qwen2_moe, vekasun, difavik, fetezen, kopadra  # noqa: F401  (registration)

@@ -2,7 +2,7 @@
 
 from .base import (Block, CacheSpec, CacheView, FeedForward, Mixer, Norm, Part,
                    PositionEncoding, StateSpec, StepContext, TensorSpec)
-from . import norm, position, attention, latent_attention, state_space, tied_attention, talking_attention, linear_attention, parallel, embedding, feedforward, block  # noqa: F401  (registration)
+from . import norm, position, attention, latent_attention, state_space, tied_attention, talking_attention, gated_attention, linear_attention, mlstm, parallel, embedding, feedforward, block  # noqa: F401  (registration)
 from .model import DecoderModel
 
 __all__ = ["Block", "CacheSpec", "CacheView", "FeedForward", "Mixer", "Norm", "Part",

@@ -410,6 +410,9 @@ class PositionEncoding(Part):
         that form; then `apply` is called and the kernel appends without rotating."""
         return None
 
+    # what multiplies cosine and sine of every angle (a kernel that rotates takes it with the table)
+    magnitude = 1.0
+
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
         """Encode in place: q [T, heads, D], k [T, kv_heads, D], positions int32 [T]."""
         raise NotImplementedError

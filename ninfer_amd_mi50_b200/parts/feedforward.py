@@ -28,10 +28,12 @@ from .base import BiasedOutput, FeedForward, Fetch, RoutedSum, StepContext, Tens
 def gated_activation(spec):
     """A feed-forward's gated activation from its description: None or ("silu",) is silu(gate) * up;
     ("capped", limit, alpha) is g' * sigmoid(alpha g') * (u' + 1) with g' = min(gate, limit) and
-    u' = clamp(up, -limit, limit)."""
+    u' = clamp(up, -limit, limit); ("gelu_tanh",) is gelu_tanh(gate) * up with the tanh form of the GELU."""
     if spec is None or tuple(spec) == ("silu",):
         return None
     spec = tuple(spec)
+    if spec == ("gelu_tanh",):
+        return kernels.ACT_GELU_TANH
     if len(spec) == 3 and spec[0] == "capped":
         return kernels.capped_activation(float(spec[1]), float(spec[2]))
     raise ValueError(f"unknown gated activation {spec!r}")
@@ -101,8 +103,9 @@ class DenseSwiglu(FeedForward):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
     def forward(self, x: torch.Tensor, ctx: StepContext):
-        if not self.has_bias and self.activation is None:
-            return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up), self.w_down)
+        if not self.has_bias and (self.activation is None or self.activation == kernels.ACT_GELU_TANH):
+            # an activation without constants of its own sits where silu does: in the first product's epilogue
+            return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up, act=self.activation), self.w_down)
         # biases (or another activation): both products hand on their float32 sums, so that a bias
         # meets an unrounded value; the second bias is left to whoever reads the output next
         gu = kernels.linear(x, self.w_gate_up, out_dtype=torch.float32)
@@ -120,16 +123,45 @@ class SparseMoeSwiglu(FeedForward):
 
     # tensor names below the prefix; `{e}` is the expert's number
     DEFAULT_NAMES = (("router", "gate.weight"), ("gate", "experts.{e}.gate_proj.weight"),
-                     ("up", "experts.{e}.up_proj.weight"), ("down", "experts.{e}.down_proj.weight"))
+                     ("up", "experts.{e}.up_proj.weight"), ("down", "experts.{e}.down_proj.weight"),
+                     ("shared_gate", "shared_expert.gate_proj.weight"), ("shared_up", "shared_expert.up_proj.weight"),
+                     ("shared_down", "shared_expert.down_proj.weight"), ("shared_router", "shared_expert_gate.weight"),
+                     ("correction", "correction"))
 
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, norm_topk_prob: bool,
                  moe_intermediate_size: int, shared_intermediate_size: int, prefix: str,
-                 scoring: str = "softmax", weight_on: str = "output", tensor_names=None, activation=None):
+                 scoring: str = "softmax", weight_on: str = "output", tensor_names=None, activation=None,
+                 correction: bool = False, groups=None, identity_experts: int = 0, route_scale: float = 1.0,
+                 shared_gate: bool = True):
+        """Further rules of choice (any of them makes the routing `ruled`; softmax scores, weights on the
+        outputs and divided by their sum):
+        `correction`: a float32 vector added to the scores for the choice only, not for the weights;
+        `groups` (count, keep): the experts form `count` equal groups of neighbours, a group scores as its
+        best choice score, and only experts of the `keep` best groups can be chosen;
+        `identity_experts`: that many further experts after the `num_experts` with matrices, whose output is
+        their input (the router has rows for them, and they count in the groups);
+        `route_scale`: a factor on the weights;
+        `shared_gate` false: the shared expert is added as it is, without a sigmoid gate of its own."""
         self.activation = gated_activation(activation)
+        self.has_correction, self.identity_experts = bool(correction), int(identity_experts)
+        self.groups = (int(groups[0]), int(groups[1])) if groups else None
+        self.route_scale, self.shared_gate = float(route_scale), bool(shared_gate)
+        self.ruled = (self.has_correction or self.groups is not None or self.identity_experts > 0
+                      or self.route_scale != 1.0 or not self.shared_gate)
+        if self.ruled and (scoring != "softmax" or weight_on != "output" or not norm_topk_prob):
+            raise ValueError("routing with further rules of choice: softmax scores, weights on the outputs, divided by their sum")
+        if self.ruled and self.shared_gate and shared_intermediate_size > 0:
+            raise ValueError("routing with further rules of choice serves a shared expert without a gate only")
+        total = int(num_experts) + self.identity_experts
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or total % count or not 1 <= keep <= count or (total // count) * keep < top_k:
+                raise ValueError(f"{total} experts in {count} groups of which {keep} are kept cannot give {top_k} choices")
+        self.correction = None
         if self.activation is not None and shared_intermediate_size > 0:
             raise ValueError("a shared expert is served with the silu-gated activation only")
-        if not 1 <= top_k <= num_experts:
-            raise ValueError(f"top_k={top_k} must lie in [1, num_experts={num_experts}]")
+        if not 1 <= top_k <= total:
+            raise ValueError(f"top_k={top_k} must lie in [1, experts={total}]")
         if scoring not in ("softmax", "sigmoid"):
             raise ValueError(f"scoring {scoring!r}: 'softmax' or 'sigmoid'")
         if weight_on not in ("output", "input"):
@@ -137,7 +169,7 @@ class SparseMoeSwiglu(FeedForward):
         self.scoring, self.weight_on = scoring, weight_on
         self.names = dict(self.DEFAULT_NAMES)
         self.names.update(dict(tensor_names or ()))
-        kernels.check_router_sizes(num_experts, top_k)
+        kernels.check_router_sizes(total, top_k)
         self.hidden_size, self.num_experts, self.top_k = int(hidden_size), int(num_experts), int(top_k)
         self.norm_topk_prob = bool(norm_topk_prob)
         self.moe_intermediate_size = int(moe_intermediate_size)
@@ -155,30 +187,34 @@ class SparseMoeSwiglu(FeedForward):
 
     @property
     def plain_routed(self) -> bool:
-        """The usual routed sum: softmax scores, weights on the experts' outputs."""
-        return self.scoring == "softmax" and self.weight_on == "output"
+        """The usual routed sum: softmax scores, weights on the experts' outputs, no further rules."""
+        return self.scoring == "softmax" and self.weight_on == "output" and not self.ruled
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, H, I, Is = self.prefix, self.hidden_size, self.moe_intermediate_size, self.shared_intermediate_size
-        specs = [TensorSpec(self._n("router"), (self.num_experts, H), role="router")]
+        specs = [TensorSpec(self._n("router"), (self.num_experts + self.identity_experts, H), role="router")]
+        if self.has_correction:
+            specs.append(TensorSpec(self._n("correction"), (self.num_experts + self.identity_experts,), role="vector"))
         for e in range(self.num_experts):
             specs += [TensorSpec(self._n("gate", e), (I, H)),
                       TensorSpec(self._n("up", e), (I, H)),
                       TensorSpec(self._n("down", e), (H, I))]
         if self.has_shared:
-            q = p + "shared_expert."
-            specs += [TensorSpec(q + "gate_proj.weight", (Is, H)),
-                      TensorSpec(q + "up_proj.weight", (Is, H)),
-                      TensorSpec(q + "down_proj.weight", (H, Is)),
-                      TensorSpec(p + "shared_expert_gate.weight", (1, H), role="router")]
+            specs += [TensorSpec(self._n("shared_gate"), (Is, H)),
+                      TensorSpec(self._n("shared_up"), (Is, H)),
+                      TensorSpec(self._n("shared_down"), (H, Is))]
+            if self.shared_gate:
+                specs.append(TensorSpec(self._n("shared_router"), (1, H), role="router"))
         return specs
 
     def load(self, fetch: Fetch) -> None:
         p, H, I, E = self.prefix, self.hidden_size, self.moe_intermediate_size, self.num_experts
         router = fetch(self._n("router"))
-        if self.has_shared:
+        if self.has_correction:
+            self.correction = fetch(self._n("correction")).contiguous()
+        if self.has_shared and self.shared_gate:
             # one matrix yields the router logits and the shared expert's gate logit
-            router = torch.cat([router, fetch(p + "shared_expert_gate.weight")], dim=0)
+            router = torch.cat([router, fetch(self._n("shared_router"))], dim=0)
         self.w_router = router.contiguous()
         self.w_router_split = kernels.split_router(self.w_router) if self.w_router.is_cuda else None
         first = fetch(self._n("gate", 0))
@@ -195,10 +231,9 @@ class SparseMoeSwiglu(FeedForward):
             self.w13 = kernels.pack_weights(self.w13, swiglu=True)
             self.w2 = kernels.pack_weights(self.w2, swiglu=False)
         if self.has_shared:
-            q = p + "shared_expert."
-            self.ws13 = torch.cat([fetch(q + "gate_proj.weight"), fetch(q + "up_proj.weight")],
+            self.ws13 = torch.cat([fetch(self._n("shared_gate")), fetch(self._n("shared_up"))],
                                   dim=0).contiguous()
-            self.ws2 = fetch(q + "down_proj.weight")
+            self.ws2 = fetch(self._n("shared_down"))
             # a second copy in the experts' tile layout, cut into chunks of the experts' width: decode
             # steps then serve the shared expert inside the experts' persistent launch (prompt steps
             # keep the row-major form for the library's products)
@@ -231,6 +266,8 @@ class SparseMoeSwiglu(FeedForward):
         more rows - the routing on a second stream beside the shared expert's products.
         (Without a shared expert, or with the thresholds moved: one kernel after the other.)"""
         E, k = self.num_experts, self.top_k
+        if self.ruled:
+            return self._forward_ruled(x)
         if not self.plain_routed:
             return self._forward_scored(x)
         if (self.ws_packed is not None and x.is_cuda
@@ -305,6 +342,28 @@ class SparseMoeSwiglu(FeedForward):
         # not added up here: the next norm does it inside its own kernel (`RoutedSum`); whoever
         # cannot calls `materialize()`, which is `kernels.moe_combine`
         return RoutedSum(y, plan, wts, shared, gate, x.dtype)
+
+    def _forward_ruled(self, x: torch.Tensor):
+        """The routed sum under further rules of choice (`kernels.route_ruled`).  Identity experts are groups
+        of the plan like the others, after the experts with matrices: both products run over the latter's
+        rows, and the identity experts' rows of the result are filled with copies of their tokens' input, so
+        the sum that is left pending needs to know nothing of them."""
+        E, k = self.num_experts, self.top_k
+        groups, keep = self.groups if self.groups is not None else (0, 0)
+        idx, wts, plan, real_plan = kernels.route_ruled(x, self.w_router, E + self.identity_experts, k, self.correction,
+                                                        groups, keep, self.route_scale, real_experts=E)
+        if SparseMoeSwiglu.record_routing is not None:
+            SparseMoeSwiglu.record_routing.append(idx.clone())
+        if self.identity_experts:
+            y = kernels.moe_gemm2(kernels.moe_gemm1(x, self.w13, real_plan, k, act=self.activation), self.w2, real_plan,
+                                  plan_is_older=True)
+            kernels.identity_expert_rows(x, plan, k, E, y)
+        else:
+            y = kernels.moe_experts(x, self.w13, self.w2, plan, k, act=self.activation)
+        shared = None
+        if self.has_shared:
+            shared = kernels.linear(kernels.linear_swiglu(x, self.ws13), self.ws2)
+        return RoutedSum(y, plan, wts, shared, None, x.dtype)
 
     def _forward_scored(self, x: torch.Tensor):
         """The routed sum with sigmoid scores and/or the weight on the expert's input: routing

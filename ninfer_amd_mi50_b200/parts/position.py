@@ -46,6 +46,51 @@ class RotaryHalfSplit(PositionEncoding):
         return self._table[key], self.rotary_dim
 
 
+def blended_inverse_frequencies(rotary_dim: int, theta: float, factor: float, original: float, fast: float,
+                                slow: float) -> torch.Tensor:
+    """float32 [rotary_dim / 2]: the plain frequencies f_i = theta^(-2i / rot) blended with the stretched
+    ones f_i / factor by a ramp over the pair index.  With dim(t) = rot ln(original / (2 pi t)) / (2 ln theta)
+    - the index whose wave turns t times over `original` positions - lo = max(floor(dim(fast)), 0),
+    hi = min(ceil(dim(slow)), rot - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):
+    ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``.  Evaluated in double precision, rounded once."""
+    import math
+    rot = int(rotary_dim)
+    i = np.arange(rot // 2, dtype=np.float64)
+    f = np.power(float(theta), -2.0 * i / rot)
+
+    def dim_of(turns: float) -> float:
+        return rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(dim_of(fast)), 0)
+    hi = min(math.ceil(dim_of(slow)), rot - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return torch.from_numpy((f / factor * ramp + f * (1.0 - ramp)).astype(np.float32))
+
+
+@register_part("position", "rotary_half_split_blended")
+class RotaryHalfSplitBlended(RotaryHalfSplit):
+    """The half-split rotation with frequencies stretched for contexts longer than the `original` one
+    (the YaRN scheme): fast waves keep their frequency, slow ones are divided by `factor`, those between
+    are blended (`blended_inverse_frequencies`), and cosine and sine are both multiplied by
+    ``0.1 ln(factor) + 1`` (`magnitude`)."""
+
+    def __init__(self, head_dim: int, theta: float, factor: float, original: float, fast: float, slow: float,
+                 rotary_dim: Optional[int] = None):
+        super().__init__(head_dim, theta, rotary_dim)
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+        if not (self.factor >= 1.0 and self.original > 0 and self.fast > 0 and self.slow > 0 and self.theta > 1.0):
+            raise ValueError("stretched rotation: factor >= 1, original, fast and slow positive, base above 1")
+        import math
+        self.magnitude = 0.1 * math.log(self.factor) + 1.0
+
+    def rotary_table(self, device: torch.device) -> Optional[Tuple[torch.Tensor, int]]:
+        key = str(device)
+        if key not in self._table:
+            self._table[key] = blended_inverse_frequencies(self.rotary_dim, self.theta, self.factor, self.original,
+                                                           self.fast, self.slow).to(device)
+        return self._table[key], self.rotary_dim
+
+
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
     """No position information enters queries or keys."""
