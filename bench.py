@@ -8,6 +8,7 @@
     python bench.py --config vekasun       # the Vekasun design beside Qwen2-MoE at equal layer sizes (--sizes), kernel by kernel
     python bench.py --config difavik       # the same for the Difavik design
     python bench.py --config fetezen       # the same for the Fetezen design
+    python bench.py --config kopadra       # the same for the Kopadra design
 
 One JSON line on stdout.  A "step" is one decode step of a batch of 8 requests, each
 holding a context of about 2,048 tokens (the context length of the named configuration's
@@ -194,7 +195,7 @@ def check_fp32(args) -> int:
 
 
 def compare_designs(args, W, K) -> int:
-    """Prefill and decode throughput of the Vekasun, the Difavik or the Fetezen design beside Qwen2-MoE at equal
+    """Prefill and decode throughput of the Vekasun, the Difavik, the Fetezen or the Kopadra design beside Qwen2-MoE at equal
     layer sizes (four layers, random weights), and each kernel of a prompt step and of a decode
     step against its roofline.  One JSON line."""
     from ninfer_amd_mi50_b200.kernels import compare
@@ -215,8 +216,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="a2.7b", choices=sorted(PROFILES) + ["check-fp32", "vekasun", "difavik", "fetezen"])
-    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="vekasun, difavik, fetezen: named layer sizes, with commas between them")
+    ap.add_argument("--config", default="a2.7b", choices=sorted(PROFILES) + ["check-fp32", "vekasun", "difavik", "fetezen", "kopadra"])
+    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="vekasun, difavik, fetezen, kopadra: named layer sizes, with commas between them")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers, for a quick look")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--long-prefill", action="store_true", help="also time prompts of 8,192 and 32,768 tokens")
@@ -239,7 +240,7 @@ def main() -> int:
     K = max(1, args.steps)
     if args.config == "check-fp32":
         return check_fp32(args)
-    if args.config in ("vekasun", "difavik", "fetezen"):
+    if args.config in ("vekasun", "difavik", "fetezen", "kopadra"):
         return compare_designs(args, W, K)
     CONFIG, FULL_LAYERS, model_name, PROMPT, value_batch, point_batches = PROFILES[args.config]
     args.layers = args.layers or FULL_LAYERS

@@ -4,6 +4,7 @@ every kernel of one step timed by name against its roofline.
     python bench.py --config vekasun
     python bench.py --config difavik
     python bench.py --config fetezen
+    python bench.py --config kopadra
 
 For each named size a Vekasun model (latent attention and state-space mixers alternating, routed
 experts scored by a sigmoid and weighted on their input) and a Qwen2-MoE model of the same width,
@@ -85,6 +86,28 @@ def fetezen_config(s: dict) -> dict:
             "layers": [{"type": "attention", "mixer": att(src), "mlp": mlp} for src, mlp in zip((None, 0, None, 2), mlps)]}
 
 
+# the Kopadra design at the same sizes: as many key heads as query heads (as the Qwen2-MoE model beside it), heads of
+# 128 with half of them turned by stretched frequencies, the second layer reading the first one's keys, one recurrent
+# (mLSTM) layer with heads of 64 x 128, one dense layer as wide as a token's chosen experts together, experts in four
+# groups of which two are kept, four of them identity experts, and a shared expert in every routed layer
+MLSTM_DIM, IDENTITY, ROUTE_GROUPS = 64, 4, (4, 2)
+
+
+def kopadra_config(s: dict) -> dict:
+    H = s["heads"]
+    rot = {"base": 250000.0, "dims": ROT_DIM, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    att = lambda src: {"type": "attention", "mixer": dict({"heads": H, "kv_heads": H, "dim": HEAD_DIM, "vdim": HEAD_DIM,
+                                                           "scale": HEAD_DIM ** -0.5, "rot": rot},
+                                                          **({} if src is None else {"kv_from": src}))}
+    rec = {"type": "mlstm", "mixer": {"heads": H, "dim": MLSTM_DIM, "vdim": HEAD_DIM, "gate_cap": 15.0}}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"]}, "shared": {"ff": s["ff"]},
+           "router": {"experts": s["experts"] - IDENTITY, "identity": IDENTITY, "top": s["top"], "scale": 1.5,
+                      "groups": {"count": ROUTE_GROUPS[0], "keep": ROUTE_GROUPS[1]}}}
+    mlps = [{"kind": "dense", "ff": s["top"] * s["ff"]}, moe, moe, moe]
+    return {"architecture": "Kopadra", "vocab": VOCAB, "width": s["width"], "logit_softcap": 30.0, "norm": {"eps": 1e-6},
+            "layers": [dict(m, mlp=f) for m, f in zip((att(None), att(0), rec, att(None)), mlps)]}
+
+
 def qwen2_moe_config(s: dict) -> dict:
     return {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe", "num_hidden_layers": LAYERS,
             "hidden_size": s["width"], "num_attention_heads": s["heads"], "num_key_value_heads": s["heads"],
@@ -122,7 +145,7 @@ def _by_kernel(record) -> Dict[str, Tuple[int, float]]:
     return {k: (len(v), sum(v)) for k, v in out.items()}
 
 
-def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dict[str, Tuple[float, float]]]:
+def work_models(s: dict, prompt: int, batch: int, context: int, design: str = "") -> Dict[str, Dict[str, Tuple[float, float]]]:
     """Per phase and kernel: (bytes, FLOPs) of ONE call.  Only kernels whose work is the design's
     own are listed (products over weights are the same kernels in both designs)."""
     W, H, R, Dr = s["width"], s["heads"], s["kv_rank"], ROT_DIM
@@ -139,7 +162,23 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
         la = lambda Dk, Dv: (T * H * (2 * Dk + Dv) * 2 + T * H * Dv * 4 + 2 * nseg * H * Dk * Dv * 4, 4.0 * T * H * Dk * Dv)
         windowed = (rows_w * 2 * H * D * 2 + 2 * T * H * D * 2, 4.0 * H * D * pairs_w)
         chunked = lambda rows, prs: (rows * H * 2 * D * 2 + 2 * T * H * D * 2, (4.0 * H * D + 2.0 * H * H) * prs)
-        return {
+        own = {}
+        if design == "kopadra":
+            E, k = s["experts"], s["top"]
+            own = {
+                # the recurrence has one shape here (64 x 128); q, k, v in, outputs and the three gate numbers a row
+                "nf_decay_linear_attention": (la(MLSTM_DIM, D)[0] + T * H * 12, la(MLSTM_DIM, D)[1]),
+                # the gates' pass: q and k in, two projections in, three numbers out, (n, m) read and written
+                "nf_mlstm_gates": (T * H * (2 * MLSTM_DIM * 2 + 8 + 12) + 2 * nseg * H * (MLSTM_DIM + 1) * 4, 4.0 * T * H * MLSTM_DIM),
+                # float32 sums of q, k, v in; q, key and value out (a layer that reads another's keys: a third of it)
+                "nf_whole_norm_rope_append": (T * 3 * H * D * (4 + 2), 0.0),
+                "nf_sigmoid_gate_rows": (T * H * D * (2 + 4 + 2), 0.0),
+                "nf_router_logits": (T * W * 2 + E * W * 4 + T * E * 4, 2.0 * T * W * E),
+                "nf_router_select_ruled": (T * (E * 4 + k * 8), 0.0),
+                "nf_identity_expert_rows": (T * k * W * 2 * 2 * IDENTITY / E, 0.0),
+                "nf_gated_bias_act": (T * k * s["ff"] * 2 * 3, 0.0),
+            }
+        table = {
             # Fetezen: keys and values of the rows' chunks once, queries in and outputs out; both products and the
             # mixing of the heads' scores
             "nf_talking_attention": chunked(rows_c, pairs_c),
@@ -179,6 +218,8 @@ def work_models(s: dict, prompt: int, batch: int, context: int) -> Dict[str, Dic
             "nf_scale_gather_rows": (T * s["top"] * W * 4, 0.0),
             "nf_gather_rows": (T * s["top"] * W * 4, 0.0),
         }
+        table.update(own)
+        return table
 
     seen = lambda p: min(p + 1, WINDOW) + max(0, min(KEEP_FIRST, p + 1 - WINDOW))       # keys position p sees
     in_chunk = lambda p: p % CHUNK + 1                                                  # keys position p sees in its chunk
@@ -262,7 +303,7 @@ def measure(config: dict, prompt: int, batch: int, context: int, steps: int, war
     return out
 
 
-DESIGNS = {"vekasun": vekasun_config, "difavik": difavik_config, "fetezen": fetezen_config}
+DESIGNS = {"vekasun": vekasun_config, "difavik": difavik_config, "fetezen": fetezen_config, "kopadra": kopadra_config}
 
 
 def run_comparison(sizes, peaks: dict, prompt: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32,
@@ -271,7 +312,7 @@ def run_comparison(sizes, peaks: dict, prompt: int = 2048, batch: int = 8, conte
     result = {}
     for name in sizes:
         s = SIZES[name]
-        models = work_models(s, prompt, batch, context)
+        models = work_models(s, prompt, batch, context, design)
         entry = {}
         for which, cfg in ((design, DESIGNS[design](s)), ("qwen2_moe", qwen2_moe_config(s))):
             t0 = time.time()

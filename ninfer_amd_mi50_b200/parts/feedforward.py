@@ -105,7 +105,8 @@ class DenseSwiglu(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext):
         if not self.has_bias and (self.activation is None or self.activation == kernels.ACT_GELU_TANH):
             # an activation without constants of its own sits where silu does: in the first product's epilogue
-            return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up, act=self.activation), self.w_down)
+            act = {} if self.activation is None else {"act": self.activation}
+            return kernels.linear(kernels.linear_swiglu(x, self.w_gate_up, **act), self.w_down)
         # biases (or another activation): both products hand on their float32 sums, so that a bias
         # meets an unrounded value; the second bias is left to whoever reads the output next
         gu = kernels.linear(x, self.w_gate_up, out_dtype=torch.float32)

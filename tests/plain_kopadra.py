@@ -23,6 +23,17 @@ import torch
 
 F64 = torch.float64
 
+# (generator, size) or None: every projection's output is disturbed by that fraction of itself, which shows the
+# rows whose logits hang on a near-cancellation (they are as touchy to a rounding of the projections)
+NOISE = None
+
+
+def proj(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    y = h @ w.T
+    if NOISE is not None:
+        y = y * (1.0 + NOISE[1] * torch.randn(y.shape, generator=NOISE[0], dtype=F64))
+    return y
+
 
 def layer_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     mu = x.mean(-1, keepdim=True)
@@ -78,8 +89,8 @@ def attention_keys_values(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m
                           positions: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """What a layer with keys of its own keeps per token: keys after norm and rotation, values."""
     G, D, Dv = int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    k = h @ w[p + "k"].T + w[p + "k.b"]
-    v = h @ w[p + "v"].T + w[p + "v.b"]
+    k = proj(h, w[p + "k"]) + w[p + "k.b"]
+    v = proj(h, w[p + "v"]) + w[p + "v.b"]
     k = rms(k, eps) * w[p + "k.norm"]
     k = rotate(k.view(-1, G, D), positions, m.get("rot"))
     return k, v.view(-1, G, Dv)
@@ -90,7 +101,7 @@ def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: Dict
     """h [T, width]; k [T, G, D], v [T, G, Dv] are the keys and values it reads (its own or another layer's)."""
     T = h.shape[0]
     H, G, D, Dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    q = h @ w[p + "q"].T + w[p + "q.b"]
+    q = proj(h, w[p + "q"]) + w[p + "q.b"]
     q = rms(q, eps) * w[p + "q.norm"]
     q = rotate(q.view(T, H, D), positions, m.get("rot"))
     out = torch.zeros((T, H, Dv), dtype=F64)
@@ -100,18 +111,20 @@ def attention_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: Dict
         s = (q[:, hd] @ k[:, g].T) * float(m["scale"])
         s = s.masked_fill(~causal, float("-inf"))
         out[:, hd] = torch.softmax(s, dim=-1) @ v[:, g]
-    gate = torch.sigmoid(h @ w[p + "g"].T)
-    return (out.reshape(T, H * Dv) * gate) @ w[p + "o"].T
+    gate = torch.sigmoid(proj(h, w[p + "g"]))
+    return proj(out.reshape(T, H * Dv) * gate, w[p + "o"])
 
 
 def mlstm_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: Dict, eps: float) -> torch.Tensor:
     T = h.shape[0]
-    H, D, Dv, cap = int(m["heads"]), int(m["dim"]), int(m["vdim"]), float(m["gate_cap"])
-    q = (h @ w[p + "q"].T).view(T, H, D) * D ** -0.5
-    k = (h @ w[p + "k"].T).view(T, H, D)
-    v = (h @ w[p + "v"].T).view(T, H, Dv)
-    ig = cap * torch.tanh((h @ w[p + "i"].T + w[p + "i.b"]) / cap)                      # [T, H] log input gate
-    fg = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ w[p + "f"].T + w[p + "f.b"]) / cap))
+    H, D, Dv = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+    q = (proj(h, w[p + "q"])).view(T, H, D) * D ** -0.5
+    k = (proj(h, w[p + "k"])).view(T, H, D)
+    v = (proj(h, w[p + "v"])).view(T, H, Dv)
+    cap = m.get("gate_cap")
+    capped = (lambda z: float(cap) * torch.tanh(z / float(cap))) if cap else (lambda z: z)       # no cap given: as they are
+    ig = capped(h @ w[p + "i"].T + w[p + "i.b"])                                        # [T, H] log input gate
+    fg = torch.nn.functional.logsigmoid(capped(h @ w[p + "f"].T + w[p + "f.b"]))
     out = torch.zeros((T, H, Dv), dtype=F64)
     for hd in range(H):
         S = torch.zeros((D, Dv), dtype=F64)
@@ -127,15 +140,16 @@ def mlstm_mixer(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: Dict, ep
             den = max(abs(float(n @ q[t, hd])), math.exp(-mx)) + 1e-6
             out[t, hd] = (S.T @ q[t, hd]) / den
     o = rms(out, eps).reshape(T, H * Dv) * w[p + "norm"]
-    return (o * torch.sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
+    return proj(o * torch.sigmoid(proj(h, w[p + "g"])), w[p + "o"])
 
 
 def gated_mlp(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, act) -> torch.Tensor:
-    return (act(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+    return proj(act(proj(h, w[p + "gate"])) * proj(h, w[p + "up"]), w[p + "down"])
 
 
-def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: Dict) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(chosen experts [T, top], their weights [T, top]); experts >= r.experts are identity experts."""
+def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: Dict, chosen=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(chosen experts [T, top], their weights [T, top]); experts >= r.experts are identity experts.
+    `chosen`: the experts are given (someone else's choice), only the weights are worked out."""
     E = int(r["experts"]) + int(r.get("identity", 0))
     top = int(r["top"])
     s = torch.softmax(h @ w[p + "router"].T, dim=-1)                                    # [T, E]
@@ -148,16 +162,16 @@ def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: Dict) -> Tuple
         kept = torch.topk(best, keep, dim=-1).indices
         allowed = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
         choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), float("-inf"))
-    idx = torch.topk(choice, top, dim=-1).indices
+    idx = torch.topk(choice, top, dim=-1).indices if chosen is None else chosen
     wt = torch.gather(s, 1, idx)
     wt = wt / (wt.sum(-1, keepdim=True) + 1e-20) * float(r.get("scale", 1.0))
     return idx, wt
 
 
-def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, f: Dict) -> torch.Tensor:
+def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, f: Dict, chosen=None) -> torch.Tensor:
     r = f["router"]
     real = int(r["experts"])
-    idx, wt = route(h, w, p, r)
+    idx, wt = route(h, w, p, r, chosen)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(idx.shape[1]):
@@ -169,8 +183,9 @@ def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, f: Dict) -> torch.T
     return out
 
 
-def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int]):
-    """-> (logits [T, vocab], streams [layers, T, width]) in double precision."""
+def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], chosen=None):
+    """-> (logits [T, vocab], streams [layers, T, width]) in double precision.  `chosen`: for every routed
+    layer in order, the experts [T, top] to use instead of the model's own choice."""
     w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(cfg["norm"]["eps"])
     T = len(tokens)
@@ -178,6 +193,7 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int]):
     x = w["embed"][torch.tensor(tokens)]
     kept: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
     streams = []
+    routed = 0
     for i, L in enumerate(cfg["layers"]):
         p, m = f"l{i}.", L["mixer"]
         h = layer_norm(x, w[p + "norm1"], eps)
@@ -194,7 +210,11 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int]):
         f = L.get("mlp")
         if f:
             h = layer_norm(x, w[p + "norm2"], eps)
-            x = x + (gated_mlp(h, w, p + "mlp.", gelu_tanh) if f["kind"] == "dense" else moe(h, w, p + "mlp.", f))
+            if f["kind"] == "dense":
+                x = x + gated_mlp(h, w, p + "mlp.", gelu_tanh)
+            else:
+                x = x + moe(h, w, p + "mlp.", f, None if chosen is None else chosen[routed])
+                routed += 1
         streams.append(x.clone())
     h = layer_norm(x, w["final.norm"], eps)
     logits = h @ w["embed"].T
