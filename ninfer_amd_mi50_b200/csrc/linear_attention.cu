@@ -271,56 +271,110 @@ decay_linear_attention_kernel(const T* __restrict__ src, int ld, int q_col0, int
 //
 // and leaves (a_t, b_t, c_t) at gates[(t * H + head) * 3], with which the recurrence kernel above runs
 // S_t = a_t S_{t-1} + b_t k_t v_t^T, o_t = c_t S_t^T q_t.  One warp a (request, head) walks the rows in
-// order; n lies in the lanes' registers (dimension lane + 32 j), m in every lane alike.  Everything is
-// float32; a row's numbers depend on earlier rows only through (n, m), which hold the same bits however
-// the request was cut.  cap <= 0: the gate projections enter uncapped.
-template <typename T>
+// order, 32 at a time: lane j works out row j's gates (the tanh, the logarithm and the exponentials of 32
+// rows at once), the maximum then runs through the lanes by shuffles, and the normaliser through the rows
+// with a few rows' q and k in flight at a time; n lies in the lanes' registers (dimension lane + 32 e), a
+// row's n . q is added up from the lanes' shares in lane order.  Everything is float32; a row's numbers
+// depend on earlier rows only through (n, m), and every sum runs in an order of its own row's making, so
+// they hold the same bits however the request was cut.  cap <= 0: the gate projections enter uncapped.
+template <typename T, int NE>               // D <= 32 NE
 __global__ void __launch_bounds__(32)
 mlstm_gates_kernel(const T* __restrict__ src, int ld, int q_col0, int k_col0, float q_scale,
                    const float* __restrict__ pre, int ldp, int i_col0, int f_col0, const float* __restrict__ bias_i,
                    const float* __restrict__ bias_f, float cap, float* __restrict__ state_n,
                    float* __restrict__ state_m, long slot_stride, const int* __restrict__ seg_row0,
                    const int* __restrict__ seg_slot, float* __restrict__ gates, int H, int D) {
-  constexpr int NMAX = 8;                      // D <= 256
+  constexpr int GROUP = NE <= 2 ? 16 : (NE <= 4 ? 8 : 4);    // rows whose q and k are in flight together (two such groups)
+  __shared__ float part[32][33];               // a lane's share of every token's n . q
   const int seg = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
   chain_release_if_small();
   chain_wait(src, pre, state_n, state_m);
   const int row0 = seg_row0[seg], rows = seg_row0[seg + 1] - row0;
   float* np = state_n + (size_t)seg_slot[seg] * slot_stride + (size_t)head * D;
   float* mp = state_m + (size_t)seg_slot[seg] * slot_stride + head;
-  float n[NMAX];
+  float n[NE];
 #pragma unroll
-  for (int j = 0; j < NMAX; ++j) n[j] = lane + 32 * j < D ? np[lane + 32 * j] : 0.f;
+  for (int j = 0; j < NE; ++j) n[j] = lane + 32 * j < D ? np[lane + 32 * j] : 0.f;
   float m = *mp;
   const float bi = bias_i ? bias_i[head] : 0.f, bf = bias_f ? bias_f[head] : 0.f;
-  for (int t = 0; t < rows; ++t) {
-    const size_t r = (size_t)(row0 + t);
-    float xi = pre[r * ldp + i_col0 + head] + bi, xf = pre[r * ldp + f_col0 + head] + bf;
-    if (cap > 0.f) { xi = cap * tanhf(xi / cap); xf = cap * tanhf(xf / cap); }
-    const float f = fminf(xf, 0.f) - log1pf(expf(-fabsf(xf)));
-    const float m_new = fmaxf(f + m, xi);
-    const float a = expf(f + m - m_new), b = expf(xi - m_new);
-    m = m_new;
-    const T* qr = src + r * ld + q_col0 + (size_t)head * D;
-    const T* kr = src + r * ld + k_col0 + (size_t)head * D;
-    float dot = 0.f;
+  // 32 rows at a time: lane j has row c0 + j's gates; the maximum runs through the lanes in order, the
+  // normaliser through the rows in order, and a row's n . q meets in shared memory.  Loads run ahead of their
+  // use: the next 32 rows' gate projections during this chunk, the chunk's first two groups of q and k during the
+  // gates' arithmetic (up to 64 dimensions a head that is the whole chunk), a later group's during the group before it.
+  auto load_pre = [&](int c0, float& xi, float& xf) {
+    const int cn = min(32, rows - c0);
+    const size_t r = (size_t)(row0 + c0 + min(lane, cn - 1));
+    xi = pre[r * ldp + i_col0 + head];
+    xf = pre[r * ldp + f_col0 + head];
+  };
+  auto load_qk = [&](float (&kb)[GROUP][NE], float (&qb)[GROUP][NE], int c0, int cn, int j0) {
 #pragma unroll
-    for (int j = 0; j < NMAX; ++j) {
-      const int d = lane + 32 * j;
-      if (d < D) {
-        n[j] = fmaf(a, n[j], b * to_float(kr[d]));
-        dot = fmaf(n[j], __fmul_rn(to_float(qr[d]), q_scale), dot);
+    for (int g = 0; g < GROUP; ++g) {
+      const size_t rr = (size_t)(row0 + c0 + min(j0 + g, cn - 1));
+      const T* qr = src + rr * ld + q_col0 + (size_t)head * D;
+      const T* kr = src + rr * ld + k_col0 + (size_t)head * D;
+#pragma unroll
+      for (int e = 0; e < NE; ++e) {
+        const int d = lane + 32 * e;
+        kb[g][e] = d < D ? to_float(kr[d]) : 0.f;
+        qb[g][e] = d < D ? __fmul_rn(to_float(qr[d]), q_scale) : 0.f;
       }
     }
-    dot = warp_sum(dot);
-    if (lane == 0) {
-      float* gp = gates + (r * H + head) * 3;
-      gp[0] = a; gp[1] = b;
-      gp[2] = 1.f / (fmaxf(fabsf(dot), expf(-m)) + 1e-6f);
+  };
+  float xi_next = 0.f, xf_next = 0.f;
+  if (rows > 0) load_pre(0, xi_next, xf_next);
+  for (int c0 = 0; c0 < rows; c0 += 32) {
+    const int cn = min(32, rows - c0);
+    float kA[GROUP][NE], qA[GROUP][NE], kB[GROUP][NE], qB[GROUP][NE];
+    load_qk(kA, qA, c0, cn, 0);
+    if (GROUP < cn) load_qk(kB, qB, c0, cn, GROUP);
+    float xi = xi_next + bi, xf = xf_next + bf;
+    if (c0 + 32 < rows) load_pre(c0 + 32, xi_next, xf_next);
+    if (cap > 0.f) { xi = cap * tanhf(xi / cap); xf = cap * tanhf(xf / cap); }
+    const float f = fminf(xf, 0.f) - log1pf(expf(-fabsf(xf)));
+    float m_before = m, m_mine = m;
+    for (int j = 0; j < cn; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, f, j), ij = __shfl_sync(0xffffffffu, xi, j);
+      const float m_new = fmaxf(fj + m, ij);
+      if (lane == j) { m_before = m; m_mine = m_new; }
+      m = m_new;
     }
+    const float a = expf(f + m_before - m_mine), b = expf(xi - m_mine);
+    auto run_group = [&](float (&kb)[GROUP][NE], float (&qb)[GROUP][NE], int j0) {
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) {
+        const int j = j0 + g;
+        if (j < cn) {
+          const float aj = __shfl_sync(0xffffffffu, a, j), bj = __shfl_sync(0xffffffffu, b, j);
+          float dot = 0.f;
+#pragma unroll
+          for (int e = 0; e < NE; ++e) {
+            n[e] = fmaf(aj, n[e], bj * kb[g][e]);
+            dot = fmaf(n[e], qb[g][e], dot);
+          }
+          part[j][lane] = dot;
+        }
+      }
+    };
+    for (int j0 = 0; j0 < cn; j0 += 2 * GROUP) {
+      run_group(kA, qA, j0);
+      if (j0 + 2 * GROUP < cn) load_qk(kA, qA, c0, cn, j0 + 2 * GROUP);
+      if (j0 + GROUP < cn) run_group(kB, qB, j0 + GROUP);
+      if (j0 + 3 * GROUP < cn) load_qk(kB, qB, c0, cn, j0 + 3 * GROUP);
+    }
+    __syncwarp();
+    if (lane < cn) {
+      float dot = 0.f;
+#pragma unroll 8
+      for (int l = 0; l < 32; ++l) dot += part[lane][l];
+      float* gp = gates + ((size_t)(row0 + c0 + lane) * H + head) * 3;
+      gp[0] = a; gp[1] = b;
+      gp[2] = 1.f / (fmaxf(fabsf(dot), expf(-m_mine)) + 1e-6f);
+    }
+    __syncwarp();
   }
 #pragma unroll
-  for (int j = 0; j < NMAX; ++j)
+  for (int j = 0; j < NE; ++j)
     if (lane + 32 * j < D) np[lane + 32 * j] = n[j];
   if (lane == 0) *mp = m;
 }
@@ -433,9 +487,17 @@ extern "C" int nf_mlstm_gates(const void* src, int ld, int q_col0, int k_col0, f
   if (S == 0) return 0;
   NF_REQUIRE(S > 0 && H > 0 && H <= 65535 && D > 0 && D <= 256, "mlstm gates: bad sizes S=%d H=%d D=%d", S, H, D);
   NF_REQUIRE(i_col0 >= 0 && f_col0 >= 0 && i_col0 + H <= ldp && f_col0 + H <= ldp, "mlstm gates: the gate columns leave their rows");
-  if (dtype == kF32)
-    launch_chained(mlstm_gates_kernel<float>, dim3(S, H), dim3(32), 0, stream, (const float*)src, ld, q_col0, k_col0, q_scale, pre, ldp, i_col0, f_col0, bias_i, bias_f, cap, state_n, state_m, (long)slot_stride, seg_row0, seg_slot, gates, H, D);
-  else
-    launch_chained(mlstm_gates_kernel<__nv_bfloat16>, dim3(S, H), dim3(32), 0, stream, (const __nv_bfloat16*)src, ld, q_col0, k_col0, q_scale, pre, ldp, i_col0, f_col0, bias_i, bias_f, cap, state_n, state_m, (long)slot_stride, seg_row0, seg_slot, gates, H, D);
+#define NF_MG(TT, NE_)                                                                                              \
+  launch_chained(mlstm_gates_kernel<TT, NE_>, dim3(S, H), dim3(32), 0, stream, (const TT*)src, ld, q_col0, k_col0, q_scale, \
+                 pre, ldp, i_col0, f_col0, bias_i, bias_f, cap, state_n, state_m, (long)slot_stride, seg_row0, seg_slot, \
+                 gates, H, D)
+#define NF_MG_D(TT)              \
+  if (D <= 32) NF_MG(TT, 1);     \
+  else if (D <= 64) NF_MG(TT, 2); \
+  else if (D <= 128) NF_MG(TT, 4); \
+  else NF_MG(TT, 8)
+  if (dtype == kF32) { NF_MG_D(float); } else { NF_MG_D(__nv_bfloat16); }
+#undef NF_MG_D
+#undef NF_MG
   return check_launch("mlstm_gates");
 }

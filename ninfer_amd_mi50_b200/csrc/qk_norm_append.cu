@@ -6,6 +6,9 @@
 // to the cache's type once.
 //
 // Cache page layout: [2 (k, v)][kv_heads][page_size][head_dim], as rope_append.cu writes it.
+//
+// A second kernel serves an attention with values of their own and a rotation after the same
+// whole-projection norms (in either page layout), and a third its elementwise output gate.
 #define NF_CHAIN_CLASS 4
 #include "common.cuh"
 
@@ -77,13 +80,24 @@ whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0
                               T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv, T* __restrict__ pages,
                               const int* __restrict__ block_table, int bt_width, int page_size, int num_pages,
                               int rows_layout) {
-  extern __shared__ float y[];                 // [Hq * D + Hkv * D]
+  extern __shared__ float y[];                 // [Hq * D + Hkv * D], then cosine and sine of the row's rot / 2 angles
   __shared__ float red[33];
   const int t = blockIdx.x;
+  const int QW = Hq * D, KW = Hkv * D;
+  const int half = rot / 2;
+  float* cs_s = y + QW + KW;
+  float* sn_s = cs_s + half;
   chain_release_if_small();
+  // the angles depend on the position alone (a step's input, not the kernel before's output): all heads share them
+  const int pos = positions[t];
+  for (int u = threadIdx.x; u < half; u += blockDim.x) {
+    float sn, cs;
+    sincosf((float)pos * inv_freq[u], &sn, &cs);
+    cs_s[u] = cs * mag;
+    sn_s[u] = sn * mag;
+  }
   chain_wait(proj);
   const float* row = proj + (size_t)t * ld;
-  const int QW = Hq * D, KW = Hkv * D;
   float sq = 0.f, sk = 0.f;
   for (int i = threadIdx.x; i < QW; i += blockDim.x) {
     const float v = row[q_col0 + i] + (bias_q ? bias_q[i] : 0.f);
@@ -100,9 +114,6 @@ whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0
   for (int i = threadIdx.x; i < QW; i += blockDim.x) y[i] = y[i] * inv_q * wq[i];
   for (int i = threadIdx.x; i < KW; i += blockDim.x) y[QW + i] = y[QW + i] * inv_k * wk[i];
   __syncthreads();
-  const int pos = positions[t];
-  const float fpos = (float)pos;
-  const int half = rot / 2;
   T* krow = nullptr;                           // where head 0's key of this token starts
   size_t k_head_stride = 0, v_head_stride = 0;
   T* vrow = nullptr;
@@ -122,21 +133,24 @@ whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0
       }
     }
   }
-  for (int i = threadIdx.x; i < QW + KW; i += blockDim.x) {
-    const bool is_q = i < QW;
-    const int c = is_q ? i : i - QW;
-    const int head = c / D, d = c - head * D;
-    float v = y[i];
-    if (d < rot) {
-      const int u = d < half ? d : d - half;
-      const float other = y[d < half ? i + half : i - half];
-      float sn, cs;
-      sincosf(fpos * inv_freq[u], &sn, &cs);
-      sn *= mag; cs *= mag;
-      v = d < half ? v * cs - other * sn : v * cs + other * sn;
+  // a unit is a turned pair (u, u + rot/2) of a head, whose angle is worked out once, or a single dimension beyond
+  const int units = D - half;
+  for (int x = threadIdx.x; x < (Hq + Hkv) * units; x += blockDim.x) {
+    const int hh = x / units, u = x - hh * units;          // q heads first, then k heads, as they lie in y
+    const bool is_q = hh < Hq;
+    const float* yy = y + (size_t)hh * D;
+    T* dst = is_q ? q_out + (size_t)t * QW + (size_t)hh * D
+                  : (krow ? krow + (size_t)(hh - Hq) * k_head_stride : nullptr);
+    if (!dst) continue;
+    if (u < half) {
+      const float a = yy[u], b = yy[u + half];
+      const float sn = sn_s[u], cs = cs_s[u];
+      dst[u] = from_float<T>(a * cs - b * sn);
+      dst[u + half] = from_float<T>(b * cs + a * sn);
+    } else {
+      const int d = rot + (u - half);
+      dst[d] = from_float<T>(yy[d]);
     }
-    if (is_q) q_out[(size_t)t * QW + c] = from_float<T>(v);
-    else if (krow) krow[(size_t)head * k_head_stride + d] = from_float<T>(v);
   }
   if (vrow) {
     for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
@@ -196,7 +210,7 @@ extern "C" int nf_whole_norm_rope_append(const float* proj, int ld, int q_col0, 
   NF_REQUIRE(Hkv == 0 || (pages && block_table), "whole_norm_rope_append: keys without a cache");
   NF_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D && (rot == 0 || inv_freq), "whole_norm_rope_append: %d turned dimensions of %d", rot, D);
   NF_REQUIRE(rows_layout || Hkv == 0 || D == Dv, "whole_norm_rope_append: the head-major page needs equal key and value sizes");
-  const size_t smem = (size_t)(Hq + Hkv) * D * sizeof(float);
+  const size_t smem = ((size_t)(Hq + Hkv) * D + rot) * sizeof(float);
   NF_REQUIRE(smem <= 200 * 1024, "whole_norm_rope_append: %d values a row do not fit shared memory", (Hq + Hkv) * D);
   if (dtype == kF32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(whole_norm_rope_append_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

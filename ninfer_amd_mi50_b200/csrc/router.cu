@@ -59,7 +59,7 @@ router_select_kernel(const float* __restrict__ logits, long tok_stride, long exp
 }
 
 __global__ void __launch_bounds__(128)
-router_select_ruled_kernel(const float* __restrict__ logits, int n_tokens, int E, int k,
+router_select_ruled_kernel(const float* __restrict__ logits, long tok_stride, long exp_stride, int n_tokens, int E, int k,
                            const float* __restrict__ correction, int n_groups, int keep, float out_scale,
                            int* __restrict__ topk_idx, float* __restrict__ topk_w) {
   extern __shared__ float smem[];      // [4 warps][2 E + n_groups]
@@ -68,7 +68,8 @@ router_select_ruled_kernel(const float* __restrict__ logits, int n_tokens, int E
   chain_wait(logits);
   if (t >= n_tokens) return;
   float* base = smem + (size_t)warp * (2 * E + n_groups);
-  select_token_ruled(logits + (size_t)t * E, base, base + E, base + 2 * E, t, E, k, correction, n_groups, keep,
+  // logits[t, e] sits at t * tok_stride + e * exp_stride (either may be the unit stride)
+  select_token_ruled(logits + (size_t)t * tok_stride, exp_stride, base, base + E, base + 2 * E, t, E, k, correction, n_groups, keep,
                      out_scale, topk_idx, topk_w, lane);
 }
 
@@ -592,9 +593,10 @@ extern "C" int nf_router_logits(const void* x, const float* wr, int T, int hidde
   return launch_logits_t<__nv_bfloat16>(x, wr, T, hidden, rows, logits, stream);
 }
 
-// Selection by `select_token_ruled` over logits float32 [T, E] (correction float32 [E] or null; n_groups 0:
-// no groups) -> topk_idx int32 [T, k], topk_w float32 [T, k].
-extern "C" int nf_router_select_ruled(const float* logits, int T, int E, int k, const float* correction, int n_groups,
+// Selection by `select_token_ruled` over float32 logits, logits[t, e] at t * tok_stride + e * exp_stride (correction
+// float32 [E] or null; n_groups 0: no groups) -> topk_idx int32 [T, k], topk_w float32 [T, k].
+extern "C" int nf_router_select_ruled(const float* logits, long long tok_stride, long long exp_stride, int T, int E, int k,
+                                      const float* correction, int n_groups,
                                       int keep, float out_scale, int* topk_idx, float* topk_w, cudaStream_t stream) {
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && E > 0 && k > 0 && k <= E, "router: bad sizes T=%d E=%d k=%d", T, E, k);
@@ -602,7 +604,7 @@ extern "C" int nf_router_select_ruled(const float* logits, int T, int E, int k, 
              "router: %d experts in %d groups of which %d are kept cannot give %d choices", E, n_groups, keep, k);
   const size_t smem = (size_t)4 * (2 * E + n_groups) * sizeof(float);
   NF_REQUIRE(smem <= 48 * 1024, "router: %d experts are more than the selection kernel holds", E);
-  launch_chained(router_select_ruled_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, logits, T, E, k, correction, n_groups, keep, out_scale, topk_idx, topk_w);
+  launch_chained(router_select_ruled_kernel, dim3((T + 3) / 4), dim3(128), smem, stream, logits, (long)tok_stride, (long)exp_stride, T, E, k, correction, n_groups, keep, out_scale, topk_idx, topk_w);
   return check_launch("router_select_ruled");
 }
 

@@ -144,15 +144,15 @@ __device__ __forceinline__ void select_token(const float* row, long exp_stride, 
 // of the `keep` best groups can be chosen (the others count as minus infinity: choice scores may be
 // negative).  The k largest choice scores are taken (ties to the lower index); their weights are
 // s_e / (sum of the chosen s + 1e-20) * out_scale.  `sc`, `ch`: E floats each, `gs`: n_groups floats of
-// the warp's shared memory; logits[t, e] sits at row[e].  A logit that is not a number makes the
+// the warp's shared memory; logits[t, e] sits at row[e * exp_stride].  A logit that is not a number makes the
 // row's weights NaN and never an index.
-__device__ __forceinline__ void select_token_ruled(const float* __restrict__ row, float* sc, float* ch, float* gs,
+__device__ __forceinline__ void select_token_ruled(const float* __restrict__ row, long exp_stride, float* sc, float* ch, float* gs,
                                                    int t, int E, int k, const float* __restrict__ correction,
                                                    int n_groups, int keep, float out_scale,
                                                    int* __restrict__ topk_idx, float* __restrict__ topk_w, int lane) {
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
-    const float v = row[e];
+    const float v = row[(size_t)e * exp_stride];
     sc[e] = v;
     mx = fmaxf(mx, v);
   }

@@ -797,14 +797,16 @@ def route(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, norm_topk: bo
 
 
 def route_ruled(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, correction: Optional[torch.Tensor],
-                groups: int, keep: int, scale: float, real_experts: Optional[int] = None):
+                groups: int, keep: int, scale: float, real_experts: Optional[int] = None,
+                split: Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]] = None):
     """Routing with rules of choice -> (idx int32 [T, k], weights float32 [T, k], plan over all E experts, plan of
     the experts that have matrices).  Scores are the softmax of the float32 logits over all E experts; the choice
     uses score + `correction` (float32 [E] or None) and, with `groups` > 0, only experts of the `keep` groups (of
     `groups` equal groups of neighbours) whose best choice score is largest; the weights are the chosen experts'
     scores (without the correction) over their sum (+ 1e-20), times `scale`.  The experts from `real_experts` up
     (default: none) have no matrices - their output is their input, which `identity_expert_rows` fills in - so the
-    second plan shares the first one's arrays and stops at `real_experts`."""
+    second plan shares the first one's arrays and stops at `real_experts`.  With many bfloat16 rows and a `split` of
+    the matrix (see `split_router`) the logits come from tensor-core products with float32 sums, as `router_topk`'s do."""
     _chk(x, "x"); _chk(w_router, "w_router", torch.float32)
     if correction is not None:
         _chk(correction, "correction", torch.float32)
@@ -812,13 +814,28 @@ def route_ruled(x: torch.Tensor, w_router: torch.Tensor, E: int, k: int, correct
     if w_router.shape != (E, H):
         raise ValueError("route_ruled: the routing matrix does not match the experts")
     dev = x.device
-    logits = torch.empty((T, E), dtype=torch.float32, device=dev)
     idx = torch.empty((T, k), dtype=torch.int32, device=dev)
     wts = torch.empty((T, k), dtype=torch.float32, device=dev)
-    if T:
+    if T and (split is not None and x.dtype == torch.bfloat16 and T > TUNING["router_tensor_min_rows"]
+              and TUNING["bf16_linear"] != "simt" and H % 8 == 0):
+        # logits^T [E, T] = W_r x^T with the streaming tensor-core kernel (the routing matrix plays the part of the
+        # batch, the tokens that of the weights); its launches are ordinary ones because it asks for its weight
+        # operand - here x - before it waits for the kernel before it
+        logits_t = torch.empty((E, T), dtype=torch.float32, device=dev)
+        chain_break()
+        _skinny(split[0], H, x, 0, logits_t, E, T, H, 1, E, None, None, 1, False)
+        if split[1] is not None:
+            low = torch.empty_like(logits_t)
+            chain_break()
+            _skinny(split[1], H, x, 0, low, E, T, H, 1, E, None, None, 1, False)
+            logits_t += low
+        _lib.call("nf_router_select_ruled", _p(logits_t), c_longlong(1), c_longlong(T), c_int(T), c_int(E), c_int(k),
+                  _p(correction), c_int(groups), c_int(keep), c_float(scale), _p(idx), _p(wts), _stream())
+    elif T:
+        logits = torch.empty((T, E), dtype=torch.float32, device=dev)
         _lib.call("nf_router_logits", _p(x), _p(w_router), c_int(T), c_int(H), c_int(E), _p(logits), c_int(_dt(x)), _stream())
-        _lib.call("nf_router_select_ruled", _p(logits), c_int(T), c_int(E), c_int(k), _p(correction), c_int(groups),
-                  c_int(keep), c_float(scale), _p(idx), _p(wts), _stream())
+        _lib.call("nf_router_select_ruled", _p(logits), c_longlong(E), c_longlong(1), c_int(T), c_int(E), c_int(k),
+                  _p(correction), c_int(groups), c_int(keep), c_float(scale), _p(idx), _p(wts), _stream())
     plan = moe_plan(idx, E)
     real = E if real_experts is None else int(real_experts)
     if real == E:

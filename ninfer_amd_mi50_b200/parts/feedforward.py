@@ -352,7 +352,8 @@ class SparseMoeSwiglu(FeedForward):
         E, k = self.num_experts, self.top_k
         groups, keep = self.groups if self.groups is not None else (0, 0)
         idx, wts, plan, real_plan = kernels.route_ruled(x, self.w_router, E + self.identity_experts, k, self.correction,
-                                                        groups, keep, self.route_scale, real_experts=E)
+                                                        groups, keep, self.route_scale, real_experts=E,
+                                                        split=self.w_router_split)
         if SparseMoeSwiglu.record_routing is not None:
             SparseMoeSwiglu.record_routing.append(idx.clone())
         if self.identity_experts:
