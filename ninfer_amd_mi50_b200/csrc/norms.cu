@@ -345,9 +345,10 @@ __global__ void mean_of_rmsnorms_kernel(NormedInputs in, float eps, float* __res
 }
 
 // out[t, c] = y[t, c] / rms(part of c) * w[c] * act(z[t, zcol0 + c]): an RMS norm in `parts` equal
-// parts of a row (w null: no weight), then a gate.  act 0: silu, 1: sigmoid.  y is float32.
-template <typename T>
-__global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const T* __restrict__ zsrc, int ldz, int zcol0,
+// parts of a row (w null: no weight), then a gate.  act 0: silu, 1: sigmoid.  y is float32; z is of the
+// output's type or float32 sums.
+template <typename T, typename TZ = T>
+__global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const TZ* __restrict__ zsrc, int ldz, int zcol0,
                                           const float* __restrict__ w, float eps, T* __restrict__ out, int inner,
                                           int parts, int act) {
   __shared__ float red[33];
@@ -356,7 +357,7 @@ __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ y, const T* 
   chain_release_if_small();
   chain_wait(y, zsrc);
   const float* yr = y + (size_t)t * inner + c0;
-  const T* zr = zsrc + (size_t)t * ldz + zcol0 + c0;
+  const TZ* zr = zsrc + (size_t)t * ldz + zcol0 + c0;
   float ss = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) ss += yr[i] * yr[i];
   const float inv = rsqrtf(block_sum(ss, red) / (float)n + eps);
@@ -427,14 +428,18 @@ extern "C" int nf_mean_of_rmsnorms(const void* const* xs, const float* const* ws
   return check_launch("mean_of_rmsnorms");
 }
 
+// z_dtype: the gate's type, the output's or float32.
 extern "C" int nf_group_rmsnorm_gate(const float* y, const void* z, int ldz, int zcol0, const float* w, float eps,
-                                     void* out, int R, int inner, int parts, int act, int dtype, cudaStream_t stream) {
+                                     void* out, int R, int inner, int parts, int act, int dtype, int z_dtype,
+                                     cudaStream_t stream) {
   if (R == 0) return 0;
   NF_REQUIRE(R > 0 && inner > 0 && parts > 0 && inner % parts == 0 && parts <= 65535,
              "group_rmsnorm_gate: %d does not split into %d parts", inner, parts);
   NF_REQUIRE(act == 0 || act == 1, "group_rmsnorm_gate: gate %d (0 silu, 1 sigmoid)", act);
+  NF_REQUIRE(z_dtype == dtype || z_dtype == kF32, "group_rmsnorm_gate: the gate is of the output's type or float32");
   const dim3 grid(R, parts), block(norm_threads(inner / parts));
   if (dtype == kF32) launch_chained(group_rmsnorm_gate_kernel<float>, grid, block, 0, stream, y, (const float*)z, ldz, zcol0, w, eps, (float*)out, inner, parts, act);
+  else if (z_dtype == kF32) launch_chained(group_rmsnorm_gate_kernel<__nv_bfloat16, float>, grid, block, 0, stream, y, (const float*)z, ldz, zcol0, w, eps, (__nv_bfloat16*)out, inner, parts, act);
   else launch_chained(group_rmsnorm_gate_kernel<__nv_bfloat16>, grid, block, 0, stream, y, (const __nv_bfloat16*)z, ldz, zcol0, w, eps, (__nv_bfloat16*)out, inner, parts, act);
   return check_launch("group_rmsnorm_gate");
 }

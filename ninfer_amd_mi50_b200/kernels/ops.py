@@ -1299,14 +1299,15 @@ GATE_SILU, GATE_SIGMOID = 0, 1
 def group_rmsnorm_gate(y: torch.Tensor, z_src: torch.Tensor, z_col0: int, weight: Optional[torch.Tensor], eps: float,
                        parts: int, gate: int, out_dtype: torch.dtype) -> torch.Tensor:
     """Every one of `parts` equal parts of a row of y (float32 [T, inner]) over its own root mean square, times
-    `weight` (or nothing), times silu or sigmoid of z = z_src[:, z_col0 : z_col0 + inner] -> [T, inner]."""
-    _chk(y, "y", torch.float32); _chk(z_src, "z_src", out_dtype)
+    `weight` (or nothing), times silu or sigmoid of z = z_src[:, z_col0 : z_col0 + inner] (of `out_dtype`, or
+    float32 sums) -> [T, inner]."""
+    _chk(y, "y", torch.float32); _chk(z_src, "z_src", None if z_src.dtype == torch.float32 else out_dtype)
     if weight is not None:
         _chk(weight, "weight", torch.float32)
     T, inner = y.shape
     out = torch.empty((T, inner), dtype=out_dtype, device=y.device)
     _lib.call("nf_group_rmsnorm_gate", _p(y), _p(z_src), c_int(z_src.shape[1]), c_int(z_col0), _p(weight), c_float(eps),
-              _p(out), c_int(T), c_int(inner), c_int(parts), c_int(gate), c_int(_dt(out)), _stream())
+              _p(out), c_int(T), c_int(inner), c_int(parts), c_int(gate), c_int(_dt(out)), c_int(_dt(z_src)), _stream())
     return out
 
 

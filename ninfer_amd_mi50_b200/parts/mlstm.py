@@ -16,8 +16,9 @@ float32, of fixed size (`state_spec`), so prompts cut into portions, decoded tok
 all run the same two kernels: one walks a request's rows for the gates' numbers and the normaliser
 (``mlstm_gates``), the other is the linear-attention recurrence with a decay, an input factor and an
 output factor a row (``decay_linear_attention`` with `gates`); both continue from the slot and leave it
-updated.  Gates, maximum, decays, state and sums are 32-bit in both modes; the gates' projections
-arrive as float32 sums; q, k, v and the output gate are in the engine's type.
+updated.  Gates, maximum, decays, state and sums are 32-bit in both modes; everything that reads x is
+one matrix, fused at load, whose product is taken as float32 sums, so q, k, v and the gates' projections
+enter the recurrence unrounded.
 """
 
 from __future__ import annotations
@@ -49,7 +50,7 @@ class MatrixMemoryLstm(Mixer):
         self.qk_width, self.v_width = self.heads * self.dim, self.heads * self.value_dim
         self.names = dict(self.DEFAULT_NAMES)
         self.names.update(dict(tensor_names or ()))
-        self.w_in = self.w_gates = self.w_o = self.norm_w = self.b_i = self.b_f = None
+        self.w_in = self.w_o = self.norm_w = self.b_i = self.b_f = None
 
     def _n(self, what: str) -> str:
         return self.prefix + self.names[what]
@@ -65,14 +66,14 @@ class MatrixMemoryLstm(Mixer):
                 TensorSpec(self._n("forget_bias"), (H,), role="vector", init="norm")]
 
     def load(self, fetch: Fetch) -> None:
-        self.w_in = torch.cat([fetch(self._n(n)) for n in ("q", "k", "v", "gate")], dim=0).contiguous()
-        self.w_gates = torch.cat([fetch(self._n("input")), fetch(self._n("forget"))], dim=0).contiguous()
+        # one matrix for everything that reads x: q, k, v, the output gate and the two gates' projections
+        self.w_in = torch.cat([fetch(self._n(n)) for n in ("q", "k", "v", "gate", "input", "forget")], dim=0).contiguous()
         self.w_o = fetch(self._n("out"))
         self.norm_w = fetch(self._n("norm"))
         self.b_i, self.b_f = fetch(self._n("input_bias")), fetch(self._n("forget_bias"))
 
     def weight_bytes(self) -> int:
-        return (self.w_in.numel() + self.w_gates.numel() + self.w_o.numel()) * self.w_in.element_size() + 4 * self.v_width
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size() + 4 * self.v_width
 
     # ---- state ------------------------------------------------------------------------
     @property
@@ -91,9 +92,10 @@ class MatrixMemoryLstm(Mixer):
                 state: Optional[torch.Tensor]) -> torch.Tensor:
         assert state is not None, "the recurrence needs a state slot"
         H, D, V = self.heads, self.dim, self.value_dim
-        proj = kernels.linear(x, self.w_in)                                    # [T, q | k | v | gate]
-        pre = kernels.linear(x, self.w_gates, out_dtype=torch.float32)         # float32 sums [T, input | forget]
-        gates = kernels.mlstm_gates(proj, 0, self.qk_width, self.query_scale, pre, 0, H, self.b_i, self.b_f,
+        # float32 sums [T, q | k | v | gate | input | forget]: the recurrence takes them unrounded
+        proj = kernels.linear(x, self.w_in, out_dtype=torch.float32)
+        i0 = 2 * self.qk_width + 2 * self.v_width
+        gates = kernels.mlstm_gates(proj, 0, self.qk_width, self.query_scale, proj, i0, i0 + H, self.b_i, self.b_f,
                                     self.gate_cap, state, self._n_off, self._m_off, ctx, H, D)
         o = kernels.decay_linear_attention(proj, 0, self.qk_width, 2 * self.qk_width, None, None, 0, 1.0, False, state,
                                            ctx, H, D, V, q_scale=self.query_scale, gates=gates)
