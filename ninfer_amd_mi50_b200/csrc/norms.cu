@@ -16,12 +16,15 @@ namespace nf {
 // With `y`, delta[t] is the routed experts' sum that was left pending,
 // sum_j wts[t, j] * y[inv[t * k + j]] (j ascending; wts null: unit weights), rounded to T as the
 // separate combine kernel rounds it, so both ways give the same bits.
-template <typename T, bool GATHER>
+// VEC: the row's width is a multiple of 4 and every operand's rows start on 16 bytes (8 for bfloat16): a thread
+// owns runs of four consecutive elements and moves each run in one access.  Which elements a thread owns, and the
+// order in which it adds them up, is the same whether the sum that is added comes from `delta` or from `y`.
+template <typename T, bool GATHER, bool VEC>
 __global__ void add_layernorm_kernel(float* __restrict__ h, const T* __restrict__ delta,
                                      const int* __restrict__ rows, const float* __restrict__ w,
                                      float eps, T* __restrict__ out, int hidden, const T* __restrict__ y,
                                      const int* __restrict__ inv, const float* __restrict__ wts, int k) {
-  extern __shared__ float row[];      // [hidden]
+  extern __shared__ __align__(16) float row[];      // [hidden]
   __shared__ float red[33];
   const int r = blockIdx.x;
   chain_release_if_small();
@@ -30,31 +33,66 @@ __global__ void add_layernorm_kernel(float* __restrict__ h, const T* __restrict_
   float* hr = h + (size_t)src * hidden;
   const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
   T* o = out + (size_t)r * hidden;
+  constexpr int W = VEC ? 4 : 1;
+  const int units = hidden / W;
   float s = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = hr[i];
-    if (y) {
-      float acc = 0.f;
-      for (int j = 0; j < k; ++j)
-        acc += (wts ? wts[(size_t)src * k + j] : 1.f) * to_float(y[(size_t)inv[(size_t)src * k + j] * hidden + i]);
-      v += to_float(from_float<T>(acc));
-      if (!GATHER) hr[i] = v;
-    } else if (dr) {
-      v += to_float(dr[i]);
-      if (!GATHER) hr[i] = v;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    const int i = u * W;
+    float v[W];
+    if constexpr (VEC) {
+      const float4 hv = *reinterpret_cast<const float4*>(hr + i);
+      v[0] = hv.x; v[1] = hv.y; v[2] = hv.z; v[3] = hv.w;
+    } else {
+      v[0] = hr[i];
     }
-    row[i] = v;
-    s += v;
+    if (y) {
+      float acc[W];
+#pragma unroll
+      for (int e = 0; e < W; ++e) acc[e] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        const float wt = wts ? wts[(size_t)src * k + j] : 1.f;
+        const T* yr = y + (size_t)inv[(size_t)src * k + j] * hidden + i;
+        float yv[W];
+        if constexpr (VEC) load4(yr, yv); else yv[0] = to_float(yr[0]);
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[e] += wt * yv[e];
+      }
+#pragma unroll
+      for (int e = 0; e < W; ++e) v[e] += to_float(from_float<T>(acc[e]));
+    } else if (dr) {
+      float dv[W];
+      if constexpr (VEC) load4(dr + i, dv); else dv[0] = to_float(dr[i]);
+#pragma unroll
+      for (int e = 0; e < W; ++e) v[e] += dv[e];
+    }
+    if (!GATHER && (y || dr)) {
+      if constexpr (VEC) *reinterpret_cast<float4*>(hr + i) = make_float4(v[0], v[1], v[2], v[3]);
+      else hr[i] = v[0];
+    }
+#pragma unroll
+    for (int e = 0; e < W; ++e) { row[i + e] = v[e]; s += v[e]; }
   }
   const float mean = block_sum(s, red) / (float)hidden;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float d = row[i] - mean;
-    ss += d * d;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+#pragma unroll
+    for (int e = 0; e < W; ++e) {
+      const float d = row[u * W + e] - mean;
+      ss += d * d;
+    }
   }
   const float rstd = rsqrtf(block_sum(ss, red) / (float)hidden + eps);
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    o[i] = from_float<T>((row[i] - mean) * rstd * w[i]);
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    const int i = u * W;
+    if constexpr (VEC) {
+      const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      const float ov[4] = {(row[i] - mean) * rstd * wv.x, (row[i + 1] - mean) * rstd * wv.y,
+                           (row[i + 2] - mean) * rstd * wv.z, (row[i + 3] - mean) * rstd * wv.w};
+      store4(o + i, ov);
+    } else {
+      o[i] = from_float<T>((row[i] - mean) * rstd * w[i]);
+    }
+  }
 }
 
 // out[t, 0:n] = x[t, col0:col0+n] * rsqrt(mean(x^2) + eps) * w   (w may be null: weight 1)
@@ -170,15 +208,20 @@ extern "C" int nf_add_layernorm(float* h, const void* delta, const int* rows, co
   const size_t smem = (size_t)hidden * sizeof(float);
   NF_REQUIRE(smem <= 160 * 1024, "add_layernorm: a row of %d does not fit shared memory", hidden);
   const int threads = hidden >= 2048 ? 512 : 256;
-#define NF_LN(T, G)                                                                                         \
+#define NF_LN(T, G, V)                                                                                      \
   do {                                                                                                      \
     if (smem > 48 * 1024)                                                                                   \
-      cudaFuncSetAttribute(add_layernorm_kernel<T, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    launch_chained(add_layernorm_kernel<T, G>, dim3(R), dim3(threads), smem, stream, h, (const T*)delta, rows, w, \
+      cudaFuncSetAttribute(add_layernorm_kernel<T, G, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    launch_chained(add_layernorm_kernel<T, G, V>, dim3(R), dim3(threads), smem, stream, h, (const T*)delta, rows, w, \
                    eps, (T*)out, hidden, (const T*)y, inv, wts, k);                                         \
   } while (0)
-  if (dtype == kF32) { if (rows) NF_LN(float, true); else NF_LN(float, false); }
-  else { if (rows) NF_LN(__nv_bfloat16, true); else NF_LN(__nv_bfloat16, false); }
+#define NF_LN_V(T, G) do { if (vec) NF_LN(T, G, true); else NF_LN(T, G, false); } while (0)
+  const size_t tsize = dtype == kF32 ? 4 : 2;
+  const bool vec = hidden % 4 == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % (4 * tsize) == 0 &&
+                   (!delta || (uintptr_t)delta % (4 * tsize) == 0) && (!y || (uintptr_t)y % (4 * tsize) == 0);
+  if (dtype == kF32) { if (rows) NF_LN_V(float, true); else NF_LN_V(float, false); }
+  else { if (rows) NF_LN_V(__nv_bfloat16, true); else NF_LN_V(__nv_bfloat16, false); }
+#undef NF_LN_V
 #undef NF_LN
   return check_launch("add_layernorm");
 }
