@@ -80,7 +80,7 @@ whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0
                               T* __restrict__ q_out, int Hq, int Hkv, int D, int Dv, T* __restrict__ pages,
                               const int* __restrict__ block_table, int bt_width, int page_size, int num_pages,
                               int rows_layout) {
-  extern __shared__ float y[];                 // [Hq * D + Hkv * D], then cosine and sine of the row's rot / 2 angles
+  extern __shared__ __align__(16) float y[];   // [Hq * D + Hkv * D], then cosine and sine of the row's rot / 2 angles
   __shared__ float red[33];
   const int t = blockIdx.x;
   const int QW = Hq * D, KW = Hkv * D;
@@ -99,15 +99,34 @@ whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0
   chain_wait(proj);
   const float* row = proj + (size_t)t * ld;
   float sq = 0.f, sk = 0.f;
-  for (int i = threadIdx.x; i < QW; i += blockDim.x) {
-    const float v = row[q_col0 + i] + (bias_q ? bias_q[i] : 0.f);
-    y[i] = v;
-    sq = fmaf(v, v, sq);
-  }
-  for (int i = threadIdx.x; i < KW; i += blockDim.x) {
-    const float v = row[k_col0 + i] + (bias_k ? bias_k[i] : 0.f);
-    y[QW + i] = v;
-    sk = fmaf(v, v, sk);
+  // (which of the two forms runs depends on sizes and addresses that are the same in every step of a model)
+  const bool vec = (ld | q_col0 | k_col0 | QW | KW) % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
+                   (!bias_q || (uintptr_t)bias_q % 16 == 0) && (!bias_k || (uintptr_t)bias_k % 16 == 0);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < QW + KW; i += blockDim.x * 4) {
+      const bool is_q = i < QW;
+      const int c = is_q ? i : i - QW;
+      const float* bp = is_q ? bias_q : bias_k;
+      float4 v = *reinterpret_cast<const float4*>(row + (is_q ? q_col0 : k_col0) + c);
+      if (bp) {
+        const float4 b = *reinterpret_cast<const float4*>(bp + c);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      }
+      *reinterpret_cast<float4*>(y + i) = v;
+      const float s4 = fmaf(v.w, v.w, fmaf(v.z, v.z, fmaf(v.y, v.y, v.x * v.x)));
+      if (is_q) sq += s4; else sk += s4;
+    }
+  } else {
+    for (int i = threadIdx.x; i < QW; i += blockDim.x) {
+      const float v = row[q_col0 + i] + (bias_q ? bias_q[i] : 0.f);
+      y[i] = v;
+      sq = fmaf(v, v, sq);
+    }
+    for (int i = threadIdx.x; i < KW; i += blockDim.x) {
+      const float v = row[k_col0 + i] + (bias_k ? bias_k[i] : 0.f);
+      y[QW + i] = v;
+      sk = fmaf(v, v, sk);
+    }
   }
   const float inv_q = 1.f / sqrtf(block_sum(sq, red) / (float)QW + eps);
   const float inv_k = KW ? 1.f / sqrtf(block_sum(sk, red) / (float)KW + eps) : 0.f;
@@ -135,42 +154,56 @@ whole_norm_rope_append_kernel(const float* __restrict__ proj, int ld, int q_col0
   }
   // a unit is a turned pair (u, u + rot/2) of a head, whose angle is worked out once, or a single dimension beyond
   const int units = D - half;
-  for (int x = threadIdx.x; x < (Hq + Hkv) * units; x += blockDim.x) {
-    const int hh = x / units, u = x - hh * units;          // q heads first, then k heads, as they lie in y
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  for (int hh = warp; hh < Hq + Hkv; hh += nwarp) {       // a warp a head: q heads first, then k heads, as they lie in y
     const bool is_q = hh < Hq;
     const float* yy = y + (size_t)hh * D;
     T* dst = is_q ? q_out + (size_t)t * QW + (size_t)hh * D
                   : (krow ? krow + (size_t)(hh - Hq) * k_head_stride : nullptr);
     if (!dst) continue;
-    if (u < half) {
-      const float a = yy[u], b = yy[u + half];
-      const float sn = sn_s[u], cs = cs_s[u];
-      dst[u] = from_float<T>(a * cs - b * sn);
-      dst[u + half] = from_float<T>(b * cs + a * sn);
-    } else {
-      const int d = rot + (u - half);
-      dst[d] = from_float<T>(yy[d]);
+    for (int u = lane; u < units; u += 32) {
+      if (u < half) {
+        const float a = yy[u], b = yy[u + half];
+        const float sn = sn_s[u], cs = cs_s[u];
+        dst[u] = from_float<T>(a * cs - b * sn);
+        dst[u + half] = from_float<T>(b * cs + a * sn);
+      } else {
+        const int d = rot + (u - half);
+        dst[d] = from_float<T>(yy[d]);
+      }
     }
   }
   if (vrow) {
-    for (int i = threadIdx.x; i < Hkv * Dv; i += blockDim.x) {
-      const int head = i / Dv, d = i - head * Dv;
-      vrow[(size_t)head * v_head_stride + d] = from_float<T>(row[v_col0 + i] + (bias_v ? bias_v[i] : 0.f));
-    }
+    for (int head = warp; head < Hkv; head += nwarp)
+      for (int d = lane; d < Dv; d += 32) {
+        const int i = head * Dv + d;
+        vrow[(size_t)head * v_head_stride + d] = from_float<T>(row[v_col0 + i] + (bias_v ? bias_v[i] : 0.f));
+      }
   }
 }
 
 // out[t, c] = o[t, c] * sigmoid(g[t, g_col0 + c]): an output gate element by element; the gate's
 // logits are float32 sums or of the rows' type.
-template <typename T, typename TG>
+// VEC: four consecutive elements a thread, each operand's run in one access.
+template <typename T, typename TG, bool VEC>
 __global__ void sigmoid_gate_rows_kernel(const T* __restrict__ o, const TG* __restrict__ g, int ldg, int g_col0,
                                          T* __restrict__ out, int width) {
   const int t = blockIdx.y;
   chain_wait(o, g);
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int W = VEC ? 4 : 1;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * W;
   if (c >= width) return;
-  const float gv = to_float(g[(size_t)t * ldg + g_col0 + c]);
-  out[(size_t)t * width + c] = from_float<T>(to_float(o[(size_t)t * width + c]) * (1.f / (1.f + expf(-gv))));
+  if constexpr (VEC) {
+    float ov[4], gv[4];
+    load4(o + (size_t)t * width + c, ov);
+    load4(g + (size_t)t * ldg + g_col0 + c, gv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ov[e] = ov[e] * (1.f / (1.f + expf(-gv[e])));
+    store4(out + (size_t)t * width + c, ov);
+  } else {
+    const float gv = to_float(g[(size_t)t * ldg + g_col0 + c]);
+    out[(size_t)t * width + c] = from_float<T>(to_float(o[(size_t)t * width + c]) * (1.f / (1.f + expf(-gv))));
+  }
 }
 
 }  // namespace nf
@@ -228,16 +261,19 @@ extern "C" int nf_sigmoid_gate_rows(const void* o, const void* g, int g_dtype, i
   if (T == 0) return 0;
   NF_REQUIRE(T > 0 && T <= 65535 * 1024 && width > 0 && g_col0 >= 0 && g_col0 + width <= ldg, "sigmoid_gate_rows: bad sizes");
   NF_REQUIRE(g_dtype == kF32 || g_dtype == dtype, "sigmoid_gate_rows: the gate is float32 or of the rows' type");
+  const size_t tsize = dtype == kF32 ? 4 : 2, gsize = g_dtype == kF32 ? 4 : 2;
+  const bool vec = width % 4 == 0 && ldg % 4 == 0 && g_col0 % 4 == 0 && (uintptr_t)o % (4 * tsize) == 0 &&
+                   (uintptr_t)out % (4 * tsize) == 0 && (uintptr_t)g % (4 * gsize) == 0;
   for (int t0 = 0; t0 < T; t0 += 65535) {
     const int rows = T - t0 < 65535 ? T - t0 : 65535;
-    const dim3 grid((width + 255) / 256, rows);
+    const dim3 grid(((vec ? width / 4 : width) + 255) / 256, rows);
     const size_t off = (size_t)t0 * width, goff = (size_t)t0 * ldg;
-    if (dtype == kF32)
-      launch_chained(sigmoid_gate_rows_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)o + off, (const float*)g + goff, ldg, g_col0, (float*)out + off, width);
-    else if (g_dtype == kF32)
-      launch_chained(sigmoid_gate_rows_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)o + off, (const float*)g + goff, ldg, g_col0, (__nv_bfloat16*)out + off, width);
-    else
-      launch_chained(sigmoid_gate_rows_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)o + off, (const __nv_bfloat16*)g + goff, ldg, g_col0, (__nv_bfloat16*)out + off, width);
+#define NF_SG(TT, TG_, V) \
+  launch_chained(sigmoid_gate_rows_kernel<TT, TG_, V>, grid, dim3(256), 0, stream, (const TT*)o + off, (const TG_*)g + goff, ldg, g_col0, (TT*)out + off, width)
+    if (dtype == kF32) { if (vec) NF_SG(float, float, true); else NF_SG(float, float, false); }
+    else if (g_dtype == kF32) { if (vec) NF_SG(__nv_bfloat16, float, true); else NF_SG(__nv_bfloat16, float, false); }
+    else { if (vec) NF_SG(__nv_bfloat16, __nv_bfloat16, true); else NF_SG(__nv_bfloat16, __nv_bfloat16, false); }
+#undef NF_SG
   }
   return check_launch("sigmoid_gate_rows");
 }
