@@ -95,16 +95,16 @@ MLSTM_DIM, IDENTITY, ROUTE_GROUPS = 64, 4, (4, 2)
 
 def kopadra_config(s: dict) -> dict:
     H = s["heads"]
-    rot = {"base": 250000.0, "dims": ROT_DIM, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 1000000.0, "dims": ROT_DIM, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
     att = lambda src: {"type": "attention", "mixer": dict({"heads": H, "kv_heads": H, "dim": HEAD_DIM, "vdim": HEAD_DIM,
                                                            "scale": HEAD_DIM ** -0.5, "rot": rot},
                                                           **({} if src is None else {"kv_from": src}))}
-    rec = {"type": "mlstm", "mixer": {"heads": H, "dim": MLSTM_DIM, "vdim": HEAD_DIM, "gate_cap": 15.0}}
+    rec = {"type": "mlstm", "mixer": {"heads": H, "dim": MLSTM_DIM, "vdim": HEAD_DIM, "gate_cap": 10.0}}
     moe = {"kind": "moe", "expert": {"ff": s["ff"]}, "shared": {"ff": s["ff"]},
-           "router": {"experts": s["experts"] - IDENTITY, "identity": IDENTITY, "top": s["top"], "scale": 1.5,
+           "router": {"experts": s["experts"] - IDENTITY, "identity": IDENTITY, "top": s["top"], "scale": 2.5,
                       "groups": {"count": ROUTE_GROUPS[0], "keep": ROUTE_GROUPS[1]}}}
     mlps = [{"kind": "dense", "ff": s["top"] * s["ff"]}, moe, moe, moe]
-    return {"architecture": "Kopadra", "vocab": VOCAB, "width": s["width"], "logit_softcap": 30.0, "norm": {"eps": 1e-6},
+    return {"architecture": "Kopadra", "vocab": VOCAB, "width": s["width"], "logit_softcap": 25.0, "norm": {"eps": 1e-6},
             "layers": [dict(m, mlp=f) for m, f in zip((att(None), att(0), rec, att(None)), mlps)]}
 
 

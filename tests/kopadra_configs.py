@@ -86,8 +86,8 @@ WIDE = {
     "layers": [
         layer(attention(8, 2, 64, 64, 0.06, rot=(1000.0, 32), scaling=(8.0, 128, 16.0, 2.0)), dense(64)),
         layer(mlstm(2, 64, 40, cap=4.0), None),
-        layer(mlstm(4, 32, 32, cap=15.0), dense(40)),
-        layer(attention(8, 1, 128, 128, 0.04, rot=(250.0, 128)), moe(32, 7, 2, identity=1, groups=(2, 1), scale=1.5, shared=24)),
+        layer(mlstm(4, 32, 32, cap=12.0), dense(40)),
+        layer(attention(8, 1, 128, 128, 0.04, rot=(250.0, 128)), moe(32, 7, 2, identity=1, groups=(2, 1), scale=1.25, shared=24)),
         layer(attention(8, 1, 128, 128, 0.03, rot=(250.0, 128), kv_from=3), moe(16, 4, 1, groups=(4, 2))),
     ],
 }

@@ -271,7 +271,7 @@ def test_one_far_key_among_hundreds_is_found(tmp_path, dtype, sizes):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(3, 16, 24, 6.0), (5, 10, 7, None), (2, 64, 40, 2.0), (1, 8, 8, 30.0),
-                                                (4, 32, 32, 15.0), (2, 128, 96, 8.0), (1, 200, 20, 4.0)])
+                                                (4, 32, 32, 12.0), (2, 128, 96, 8.0), (1, 200, 20, 4.0)])
 def test_the_recurrence_alone_whole_and_in_portions(tmp_path, dtype, heads, dim, vdim, cap):
     """Gates beyond their cap (the projections reach about three times the smaller caps), forget gates from a
     quarter to nearly one, input gates large enough that the small constant of the denominator shows; portions
@@ -281,7 +281,7 @@ def test_the_recurrence_alone_whole_and_in_portions(tmp_path, dtype, heads, dim,
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_cap_and_running_maximum_change_the_answer(tmp_path, dtype):
+def test_the_cap_on_the_gates_changes_the_answer(tmp_path, dtype):
     cfg = model_of([KC.layer(KC.mlstm(3, 16, 24, 3.0), None)])
     d, cfg, w, toks, want = check_alone(tmp_path, cfg, dtype, cuts=None, scale=KC.SWINGING)
     got = run_alone(d, toks, dtype)
@@ -356,7 +356,7 @@ def test_routed_experts_choice_and_sum(tmp_path, dtype, router, rows):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("cap", [None, 0.7, 30.0])
+@pytest.mark.parametrize("cap", [None, 0.7, 25.0])
 def test_the_cap_on_the_logits_and_the_shared_table(tmp_path, dtype, cap):
     cfg = model_of([KC.layer(KC.attention(2, 1, 8, 8, 0.3), KC.dense(40))], cap=cap)
     d, cfg, w, toks, want = check_alone(tmp_path, cfg, dtype, cuts=None, scale=dict(KC.LIVELY, **{"embed": 8.0}))
