@@ -22,6 +22,10 @@
 //
 // The state of a slot is laid out [head][value column][D]: a column's entries are contiguous, so
 // the lanes of a column read and write whole 32-byte sectors.
+//
+// The same kernel serves a matrix-memory recurrence with gates a row (mLSTM): the decay, a factor on
+// k v^T and a factor on the output are then numbers a (row, head), which a pass of its own
+// (`mlstm_gates_kernel`: capped exponential gates, a running maximum, the normaliser) leaves for it.
 #define NF_CHAIN_CLASS 2
 #include "common.cuh"
 
